@@ -94,10 +94,13 @@ class PageAllocator:
 @dataclasses.dataclass(frozen=True)
 class KVNeed:
     """What a caching part asks of the cache: heads and width of its keys and values, and the
-    window it reads (None: all keys)."""
+    window it reads (None: all keys).  ``value_dim``: width of the values kept beside the keys
+    (None: as wide as the keys; 0: none are kept, for a part whose values are read out of the key
+    rows themselves, as a latent attention's are)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
 
 
 @dataclasses.dataclass(frozen=True)
@@ -111,8 +114,8 @@ class KVGroup:
     """Storage of the layers that share one ``KVNeed``.
 
     ``k``: ``[layers, pages + 1, kv_heads, page_size, head_dim]``; ``v`` is kept transposed inside
-    a page, ``[layers, pages + 1, kv_heads, head_dim, page_size]``, so that attention's second
-    product also contracts over the contiguous axis.
+    a page, ``[layers, pages + 1, kv_heads, value_dim, page_size]``, so that attention's second
+    product also contracts over the contiguous axis (``[layers, 0]`` for a need that keeps no values).
     ``page_table``: ``[slots + 1, table_width]`` int32; position ``p`` of the sequence in slot ``s``
     lives in page ``page_table[s, (p // page_size) % table_width]`` at offset ``p % page_size``.
     For a group that keeps all keys the table is as wide as the longest sequence; for a window it
@@ -131,7 +134,8 @@ class KVGroup:
         self.pages = PageAllocator(n_pages)
         shape = (n_layers, n_pages + 1, need.num_kv_heads, page_size, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape[:3] + (need.head_dim, page_size), dtype=dtype, device=device)
+        vdim = need.head_dim if need.value_dim is None else need.value_dim
+        self.v = torch.zeros(shape[:3] + (vdim, page_size) if vdim else (n_layers, 0), dtype=dtype, device=device)
         # row n_slots stays all zero: padded rows of a batch use it and land in page 0
         self.table_host = torch.zeros((n_slots + 1, self.table_width), dtype=torch.int32)
         self.page_table = torch.zeros((n_slots + 1, self.table_width), dtype=torch.int32, device=device)

@@ -48,8 +48,12 @@ def known_architectures() -> list:
 
 def architecture_name(raw: dict) -> str:
     """The name a config.json selects its model by: the first known entry of ``architectures``,
-    else ``model_type`` at the root or under ``text_config`` (src/config.rs:350-365)."""
+    else ``architecture`` (one name), else ``model_type`` at the root or under ``text_config``
+    (src/config.rs:350-365)."""
     _builtin()
+    one = raw.get("architecture")
+    if isinstance(one, str) and one in _ARCHITECTURES:
+        return one
     archs = raw.get("architectures")
     if isinstance(archs, list):
         for a in archs:
@@ -62,7 +66,9 @@ def architecture_name(raw: dict) -> str:
         return mt
     if isinstance(archs, list) and archs:
         return str(archs[0])
-    raise ConfigError("config.json has neither architectures nor model_type")
+    if isinstance(one, str):
+        return one
+    raise ConfigError("config.json has neither architectures, architecture nor model_type")
 
 
 def resolve_architecture(raw: dict) -> Architecture:

@@ -802,6 +802,158 @@ def attention_prefill_tc_status(head_dim: int = 0, reset: bool = True) -> int:
     return _status("gb_attention_prefill_tc_status", reset)
 
 
+# --------------------------------------------------------------------------- latent attention
+
+def latent_prepare(q_in, kv_in, g_in, norm_w, eps, inv_freq, rot, q_scale, q_nope, q_lat, gate, cache, page_table,
+                   page_size, tok_pos, tok_seq, seq_slot, heads, dim, rd, rank):
+    """From the float32 projections of a latent attention layer: the cache row of every token
+    (RMS-normed latent ``kv_in[:, :rank]``, then the key part ``kv_in[:, rank:]`` with its first
+    ``rot`` dims rotated as interleaved pairs) into the paged ``cache`` [pages, page_size, rank + rd];
+    the queries' unrotated dims times ``q_scale`` into ``q_nope`` [T, heads * dim], their rotated
+    dims (rotated, scaled) into the last ``rd`` columns of each head of ``q_lat``
+    [T, heads * (rank + rd)]; ``gate`` [T, heads] = sigmoid(g_in) (float32; None: no gate)."""
+    _cuda(q_in, kv_in, g_in, norm_w, inv_freq, q_nope, q_lat, gate, cache, page_table, tok_pos, tok_seq, seq_slot)
+    t = q_in.shape[0]
+    assert q_in.dtype == torch.float32 and kv_in.dtype == torch.float32 and q_in.stride(1) == 1 and kv_in.stride(1) == 1
+    assert q_in.shape[1] == heads * (dim + rd) and kv_in.shape == (t, rank + rd) and norm_w.numel() == rank
+    assert q_nope.shape == (t, heads * dim) and q_lat.shape == (t, heads * (rank + rd)) and q_nope.dtype == q_lat.dtype
+    assert q_nope.stride(1) == 1 and q_lat.stride(1) == 1 and norm_w.dtype == torch.float32
+    if g_in is not None:
+        assert g_in.dtype == torch.float32 and g_in.shape == (t, heads) and g_in.stride(1) == 1
+        assert gate.dtype == torch.float32 and gate.shape == (t, heads) and gate.is_contiguous()
+    if cache is not None:
+        assert cache.dtype == q_lat.dtype and cache.is_contiguous() and cache.shape[-2:] == (page_size, rank + rd)
+    if rot:
+        assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot // 2
+    f = _fn("latent_attention", "gb_latent_prepare",
+            [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_int, c_float,
+             c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(q_in.data_ptr(), q_in.stride(0), kv_in.data_ptr(), kv_in.stride(0), _ptr(g_in),
+             g_in.stride(0) if g_in is not None else 0, norm_w.data_ptr(), eps, _ptr(inv_freq), rot, q_scale,
+             q_nope.data_ptr(), q_nope.stride(0), q_lat.data_ptr(), q_lat.stride(0), _ptr(gate), _ptr(cache),
+             dtype_code(q_lat.dtype), _ptr(page_table), page_table.shape[1] if page_table is not None else 1, page_size,
+             tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), t, heads, dim, rd, rank, _stream()),
+           "latent_prepare", "elementwise", _nbytes(q_in, kv_in, q_nope) + t * (rank + 2 * rd) * q_lat.element_size())
+
+
+def heads_gemm(x, w, y, heads, scale=None):
+    """y[t, h, :] = scale[t, h] * w[h] @ x[t, h, :] for every head: x [T, heads, K] and y [T, heads, N]
+    as views of 2-D tensors (the head stride may be wider than K or N), w [heads, N, K] contiguous,
+    scale float32 [T, heads] or None.  Float32 accumulation in ascending k."""
+    _cuda(x, w, y, scale)
+    t, _, k = x.shape
+    n = w.shape[1]
+    assert x.shape[1] == heads and w.shape == (heads, n, k) and y.shape == (t, heads, n) and w.is_contiguous()
+    assert x.stride(2) == 1 and y.stride(2) == 1 and x.dtype == w.dtype == y.dtype
+    if scale is not None:
+        assert scale.dtype == torch.float32 and scale.shape == (t, heads) and scale.is_contiguous()
+    f = _fn("latent_attention", "gb_heads_gemm",
+            [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_void_p])
+    _check(f(x.data_ptr(), x.stride(0), x.stride(1), w.data_ptr(), y.data_ptr(), y.stride(0), y.stride(1), _ptr(scale),
+             dtype_code(x.dtype), t, heads, n, k, _stream()), "heads_gemm", "matmul",
+           _nbytes(w) + t * heads * (n + k) * x.element_size())
+
+
+def latent_attention_ref(qa, out, heads, rank, rd, cache, page_table, page_size, tok_pos, tok_seq, seq_slot, window=None,
+                         cache_bytes: int = 0):
+    """Causal attention of the absorbed queries qa [T, heads * (rank + rd)] over the cached rows
+    [pages, page_size, rank + rd]; out [T, heads * rank] = the softmax-weighted sums of the rows'
+    first ``rank`` dims.  One block per (token, head), float32 arithmetic, any precision."""
+    _cuda(qa, out, cache, page_table, tok_pos, tok_seq, seq_slot)
+    assert qa.stride(-1) == 1 and out.stride(-1) == 1 and qa.dtype == out.dtype == cache.dtype and cache.is_contiguous()
+    assert qa.shape[1] == heads * (rank + rd) and out.shape[1] == heads * rank and cache.shape[-1] == rank + rd
+    f = _fn("latent_attention", "gb_latent_attention_ref",
+            [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(qa.data_ptr(), qa.stride(0), out.data_ptr(), out.stride(0), dtype_code(qa.dtype), cache.data_ptr(),
+             page_table.data_ptr(), page_table.shape[1], page_size, tok_pos.data_ptr(), tok_seq.data_ptr(),
+             seq_slot.data_ptr(), qa.shape[0], heads, rank, rd, window or 0, _stream()), "latent_attention_ref",
+           "attention", _nbytes(qa, out) + cache_bytes)
+
+
+def rope_pairs(x, tok_pos, inv_freq, rot):
+    """Rotates, in place, the first ``rot`` dims of every head of x [T, heads, hd] as interleaved
+    pairs (2i, 2i + 1) by the angle float32(position) * inv_freq[i]."""
+    _cuda(x, tok_pos, inv_freq)
+    t, heads, hd = x.shape
+    assert x.stride(2) == 1 and x.stride(1) == hd and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot // 2
+    f = _fn("latent_attention", "gb_rope_pairs", [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                  c_int, c_void_p])
+    _check(f(x.data_ptr(), x.stride(0), dtype_code(x.dtype), tok_pos.data_ptr(), inv_freq.data_ptr(), t, heads, hd, rot,
+             _stream()), "rope_pairs", "elementwise", 2 * t * heads * rot * x.element_size())
+
+
+def latent_attention(ctx, qa, out, heads, rank, rd, cache, page_table, page_size, window=None):
+    """Latent attention of the step's queries over the cache; picks the kernel for the precision
+    and the sizes.  float32 always takes the plain kernel."""
+    cached = 0
+    if _profile["on"] and ctx.host is not None:
+        per_pos = (rank + rd) * cache.element_size()
+        for start, n in zip(ctx.host["seq_start"], ctx.host["seq_len"]):
+            cached += per_pos * (min(start + n, window + n - 1) if window else start + n)
+    latent_attention_ref(qa, out, heads, rank, rd, cache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
+                         window, cache_bytes=cached)
+
+
+def latent_attention_units(compute: str, rank: int, rd: int):
+    return [("latent_attention", ())]
+
+
+# --------------------------------------------------------------------------- routed feed-forward
+
+def moe_route(h, router, bias, shared_gate, top):
+    """(idx int32 [T, top], weights float32 [T, top], shared float32 [T] or None): each token's
+    ``top`` largest router logits (router [E, width] and bias [E] in float32; the lower index wins
+    a tie), the softmax over those alone, and sigmoid(shared_gate . h) when a gate row is given."""
+    _cuda(h, router, bias, shared_gate)
+    t, width = h.shape
+    e = router.shape[0]
+    assert router.dtype == torch.float32 and router.shape == (e, width) and router.is_contiguous() and h.stride(1) == 1
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == e)
+    assert shared_gate is None or (shared_gate.dtype == torch.float32 and shared_gate.numel() == width)
+    idx = torch.empty((t, top), dtype=torch.int32, device=h.device)
+    wts = torch.empty((t, top), dtype=torch.float32, device=h.device)
+    sg = torch.empty((t,), dtype=torch.float32, device=h.device) if shared_gate is not None else None
+    f = _fn("moe", "gb_moe_route", [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(h.data_ptr(), h.stride(0), dtype_code(h.dtype), router.data_ptr(), _ptr(bias), _ptr(shared_gate),
+             idx.data_ptr(), wts.data_ptr(), _ptr(sg), t, width, e, top, _stream()), "moe_route", "matmul",
+           _nbytes(h, router))
+    return idx, wts, sg
+
+
+def moe_experts(h, idx, wts, sg, w_gate_up, w_down, shared_gate_up, shared_down, residual, limit, shared_limit, alpha,
+                shift):
+    """residual[t] += sum_k wts[t, k] * expert_{idx[t, k]}(h[t]) + sg[t] * shared(h[t]), token-major
+    (two kernels: gate/up with the activation, then down).  w_gate_up [E, 2 ff, width] (gate rows,
+    then up rows), w_down [E, width, ff]; the shared expert's [2 ffs, width] and [width, ffs], or None."""
+    _cuda(h, idx, wts, sg, w_gate_up, w_down, shared_gate_up, shared_down, residual)
+    t, width = h.shape
+    e, ff2, _ = w_gate_up.shape
+    ff = ff2 // 2
+    top = idx.shape[1]
+    ffs = shared_down.shape[1] if shared_down is not None else 0
+    assert w_gate_up.is_contiguous() and w_down.is_contiguous() and w_down.shape == (e, width, ff)
+    assert w_gate_up.dtype == h.dtype == w_down.dtype and residual.dtype == torch.float32 and residual.stride(1) == 1
+    assert (shared_gate_up is None) == (shared_down is None) == (sg is None)
+    if shared_down is not None:
+        assert shared_gate_up.shape == (2 * ffs, width) and shared_gate_up.is_contiguous() and shared_down.is_contiguous()
+    slots = top + (1 if shared_down is not None else 0)
+    y = torch.empty((t, slots, max(ff, ffs)), dtype=h.dtype, device=h.device)
+    f = _fn("moe", "gb_moe_gate_up", [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                      c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_void_p])
+    _check(f(h.data_ptr(), h.stride(0), dtype_code(h.dtype), idx.data_ptr(), w_gate_up.data_ptr(), _ptr(shared_gate_up),
+             y.data_ptr(), t, width, ff, ffs, top, limit, shared_limit, alpha, shift, _stream()), "moe_gate_up", "matmul",
+           _nbytes(h, y) + t * slots * 2 * ff * width * h.element_size())
+    f = _fn("moe", "gb_moe_down", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
+                                   c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(y.data_ptr(), dtype_code(h.dtype), idx.data_ptr(), wts.data_ptr(), _ptr(sg), w_down.data_ptr(),
+             _ptr(shared_down), residual.data_ptr(), residual.stride(0), t, width, ff, ffs, top, _stream()), "moe_down",
+           "matmul", _nbytes(y) + 2 * t * width * 4 + t * slots * ff * width * h.element_size())
+
+
 # --------------------------------------------------------------------------- sampling
 
 _sample_scratch = {}

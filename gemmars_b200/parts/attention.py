@@ -119,8 +119,10 @@ class Attention(Part):
         nkv = self.num_kv_heads if self.has_kv else 0
         group, kc, vc = caches[0]
         writes_cache = writes_cache and self.has_kv
-        rotary = self.position is None or isinstance(self.position, Rotary)
-        rot = self.position.rotary_dim if isinstance(self.position, Rotary) else 0
+        # the kernels of this part rotate halves; any other encoding runs through the part's own apply
+        fused = isinstance(self.position, Rotary) and self.position.layout == "half"
+        rotary = self.position is None or fused
+        rot = self.position.rotary_dim if fused else 0
         if rotary and ctx.max_new <= 1 and kernels.gemm_qkv_usable(h, self.qkv.weight, nh, nkv, hd, rot):
             # a decode step with heads of 128: norm, rotation, scale and the cache write ride on the
             # q/k/v product's epilogue
@@ -155,7 +157,7 @@ class Attention(Part):
             store |= kernels.FLAG_SINGLE       # a decode step: one position of each sequence
         common = (ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, group.page_table, group.page_size,
                   kc if writes_cache else None, vc if writes_cache else None)
-        if self.position is None or isinstance(self.position, Rotary):
+        if rotary:
             rope = kernels.FLAG_ROPE if self.position is not None else 0
             rot = self.position.rotary_dim if rope else 0
             inv_freq = self.position.inv_freq(h.device) if rope else None

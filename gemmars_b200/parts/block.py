@@ -1,9 +1,9 @@
 """The arrangement of a layer's parts.
 
 ``prenorm`` (src/qwen.rs:682-696): x += mixer(norm(x)); x += ffn(norm(x)), the residual stream
-``x`` in float32.  Another arrangement (post-norm, parallel branches, a third norm) is another
-class like this one, registered under its own kind and reading its own part names from the
-layer's spec."""
+``x`` in float32.  ``parallel``: x += mixer(norm(x)) + ffn(norm(x)) with one norm.  Another
+arrangement (post-norm, a third norm) is another class like these, registered under its own kind
+and reading its own part names from the layer's spec."""
 from __future__ import annotations
 
 from .. import kernels
@@ -50,8 +50,34 @@ class PreNormBlock(Block):
         return None
 
 
+class ParallelBlock(Block):
+    """``parallel``: h = norm(x); x += mixer(h) + ffn(h).  One norm, and both branches read its
+    output; each branch adds its result into the float32 residual stream, the mixer first.  The
+    layer's spec lists ``norm``, ``mixer`` and, when the layer has a feed-forward, ``ffn``."""
+
+    def __init__(self, layer_spec, compute):
+        super().__init__(layer_spec, compute)
+        self.norm = self.need("norm", "norm")
+        self.mixer = self.need("mixer", "mixer")
+        self.ffn = self.need("ffn", "ffn") if "ffn" in layer_spec.parts else None
+
+    def parts(self):
+        out = {"norm": self.norm, "mixer": self.mixer}
+        if self.ffn is not None:
+            out["ffn"] = self.ffn
+        return out
+
+    def forward(self, ctx, x, caches, writes_cache=True):
+        mine = self.split_caches(caches)
+        h = self.norm.forward(ctx, x)        # read by both branches before either changes x
+        self.mixer.forward(ctx, h, x, mine["mixer"], writes_cache)
+        if self.ffn is not None:
+            self.ffn.forward(ctx, h, x)
+
+
 def _plain(h):
     return h.materialize() if isinstance(h, kernels.UnscaledRows) else h
 
 
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "parallel", ParallelBlock)

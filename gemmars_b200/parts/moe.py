@@ -1,0 +1,94 @@
+"""Routed feed-forward (mixture of experts) with an optional shared expert.
+
+    z        = router h + bias                      float32
+    chosen   = the ``top`` largest z;  weights = softmax over the chosen z alone
+    expert   : g = min(gate h, limit), u = clamp(up h, -limit, limit)
+               y = g * sigmoid(alpha g) * (u + shift);  out = down y        (no biases)
+    residual += sum over chosen of weight * expert(h)  +  sigmoid(shared_gate . h) * shared(h)
+
+The experts' matrices are stacked at load ([experts, 2 ff, hidden]: gate rows then up rows, and
+[experts, hidden, ff]) so that a kernel finds an expert by its index alone.  Parameters:
+hidden_size, experts, top, ff, limit, alpha (1.702), shift (1.0), router_bias, and ``shared``
+(None, or {"ff", "limit", "gate"}: its width, its clamp, and whether its output is multiplied by
+a sigmoid of one number per token).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from .base import Part, TensorWant, register_part
+
+
+class RoutedExperts(Part):
+    category = "ffn"
+
+    def __init__(self, spec, compute):
+        super().__init__(spec, compute)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.experts = int(p["experts"])
+        self.top = int(p["top"])
+        self.ff = int(p["ff"])
+        self.limit = float(p["limit"])
+        self.alpha = float(p.get("alpha", 1.702))
+        self.shift = float(p.get("shift", 1.0))
+        self.router_bias = bool(p.get("router_bias", True))
+        shared = p.get("shared")
+        self.shared_ff = int(shared["ff"]) if shared else 0
+        self.shared_limit = float(shared["limit"]) if shared else 0.0
+        self.shared_gated = bool(shared.get("gate", True)) if shared else False
+        if not 1 <= self.top <= min(self.experts, 32):
+            raise ValueError(f"moe: top {self.top} of {self.experts} experts is not supported (1 to 32, at most all)")
+        self.router = self.bias = self.gate_up = self.down = None
+        self.shared_gate_up = self.shared_down = self.shared_gate = None
+
+    def wants(self):
+        h, f = self.hidden_size, self.ff
+        w = {"router": TensorWant((self.experts, h), "vector")}
+        if self.router_bias:
+            w["router_bias"] = TensorWant((self.experts,), "vector")
+        for e in range(self.experts):
+            w[f"e{e}.gate"] = TensorWant((f, h))
+            w[f"e{e}.up"] = TensorWant((f, h))
+            w[f"e{e}.down"] = TensorWant((h, f))
+        if self.shared_ff:
+            fs = self.shared_ff
+            w.update({"shared.gate": TensorWant((fs, h)), "shared.up": TensorWant((fs, h)),
+                      "shared.down": TensorWant((h, fs))})
+            if self.shared_gated:
+                w["shared.sg"] = TensorWant((1, h), "vector")
+        return w
+
+    def load(self, t):
+        self.router = t["router"].contiguous()
+        self.bias = t["router_bias"].contiguous() if self.router_bias else None
+        self.gate_up = torch.stack([torch.cat([t[f"e{e}.gate"], t[f"e{e}.up"]], dim=0) for e in range(self.experts)])
+        self.down = torch.stack([t[f"e{e}.down"] for e in range(self.experts)])
+        if self.shared_ff:
+            self.shared_gate_up = torch.cat([t["shared.gate"], t["shared.up"]], dim=0).contiguous()
+            self.shared_down = t["shared.down"].contiguous()
+            if self.shared_gated:
+                self.shared_gate = t["shared.sg"].reshape(-1).contiguous()
+            else:   # sigmoid(30) is 1 in float32: an ungated shared expert is one whose gate is always open
+                self.shared_gate = None
+
+    def kernel_units(self):
+        return [("moe", ())]
+
+    def weight_bytes(self):
+        """What a decode step of one token reads: the router, ``top`` experts, the shared expert."""
+        per = self.gate_up.element_size()
+        one = 3 * self.ff * self.hidden_size * per
+        shared = 3 * self.shared_ff * self.hidden_size * per
+        return 4 * self.router.numel() + self.top * one + shared
+
+    def forward(self, ctx, h, residual):
+        idx, wts, sg = kernels.moe_route(h, self.router, self.bias, self.shared_gate, self.top)
+        if self.shared_ff and sg is None:
+            sg = torch.ones((h.shape[0],), dtype=torch.float32, device=h.device)
+        kernels.moe_experts(h, idx, wts, sg, self.gate_up, self.down, self.shared_gate_up, self.shared_down, residual,
+                            self.limit, self.shared_limit, self.alpha, self.shift)
+
+
+register_part("ffn", "moe", RoutedExperts)

@@ -1,11 +1,14 @@
-"""Rotary position encoding (rotate-half) over the first ``rotary_dim`` dims of each head.
+"""Rotary position encoding over the first ``rotary_dim`` dims of each head.
 
 inv_freq[i] = float32(1 / theta^(2i / rotary_dim)), computed in float64 (src/qwen.rs:529-533);
 angle = float32(position) * inv_freq[i] in float32 (src/kernels.rs:1525-1531);
-(a, b) = (v[i], v[i + half]) -> (a cos - b sin, b cos + a sin) (src/kernels.rs:1538-1548).
+the pair (a, b) -> (a cos - b sin, b cos + a sin) (src/kernels.rs:1538-1548).  Which dims make
+pair i is the ``layout``: "half" pairs v[i] with v[i + rotary_dim / 2] (the default), "interleaved"
+pairs v[2i] with v[2i + 1].
 
-The attention part fuses this rotation into its q/k kernel when its position encoding is this
-class; ``apply`` is the stand-alone form with the same kernel."""
+The attention part fuses the "half" rotation into its q/k kernel when its position encoding is
+this class, and the latent attention part the "interleaved" one into the kernel that writes its
+cache rows; ``apply`` is the stand-alone form of either."""
 from __future__ import annotations
 
 import torch
@@ -22,6 +25,9 @@ class Rotary(Part):
         self.head_dim = int(spec.params["head_dim"])
         self.rotary_dim = int(spec.params.get("rotary_dim", self.head_dim))
         self.theta = float(spec.params["theta"])
+        self.layout = spec.params.get("layout", "half")
+        if self.layout not in ("half", "interleaved"):
+            raise ValueError(f"rotary: unknown layout {self.layout!r} (half or interleaved)")
         if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary: cannot rotate {self.rotary_dim} of {self.head_dim} dimensions")
         i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
@@ -36,11 +42,12 @@ class Rotary(Part):
         return t
 
     def kernel_units(self):
-        return [("elementwise", ())]
+        return [("elementwise", ())] if self.layout == "half" else [("latent_attention", ())]
 
     def table(self, ctx) -> torch.Tensor:
         """(cos, sin) of the step's packed tokens' angles, [tokens, rotary_dim / 2, 2] float32,
         computed once a step and shared by every layer with the same rotation."""
+        assert self.layout == "half"
         key = ("rope_table", self.rotary_dim, self.theta)
         t = ctx.extras.get(key)
         if t is None:
@@ -51,6 +58,10 @@ class Rotary(Part):
         """Rotates q [T, nh, hd] and k [T, nkv, hd] (contiguous views) in place."""
         for x in (q, k):
             t, heads, hd = x.shape
+            if self.layout == "interleaved":
+                if self.rotary_dim:
+                    kernels.rope_pairs(x, ctx.tok_pos, self.inv_freq(x.device), self.rotary_dim)
+                continue
             flat = x.view(t, heads * hd)
             # all heads are treated as "q" heads of one tensor: rotate in place, scale 1
             kernels.head_norm_rope_cache(flat, heads, 0, hd, self.rotary_dim, None, None, 0.0,
