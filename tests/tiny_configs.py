@@ -62,3 +62,39 @@ SMALL_64 = {
 # or a tensor rounded in the wrong place shows; a single wrong low bit does not, and is what the
 # kernel tests are for (2^-7 to 2^-8 of the result against float32, with planted far keys).
 TOL_BF16 = {"A": 6e-3, "B": 1e-2, "S128": 1.2e-2}
+
+
+def _toretar_layer(heads, dim, rot_dim, vdim, rank, scale, base, rot_dims, mlp):
+    return {"type": "latent_attention",
+            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank, "scale": scale,
+                      "rot": {"base": base, "dims": rot_dims}},
+            "mlp": mlp}
+
+
+def _toretar_moe(experts, top, ff, limit, shared):
+    return {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff, "limit": limit},
+            "shared": shared}
+
+
+# Toretar: three layers that differ in every size; only part of the rotated dims turn in the
+# first; the second has no feed-forward; the third has no shared expert and chooses one expert.
+# No size is a multiple of 8 in the first layer's mixer, so the kernels for unaligned rows run.
+TORETAR_A = {
+    "architecture": "Toretar", "vocab": 301, "width": 72, "norm": {"eps": 1e-5},
+    "layers": [
+        _toretar_layer(3, 20, 6, 28, 36, 0.21, 10000.0, 4, _toretar_moe(5, 2, 40, 0.7, {"ff": 56, "limit": 1.5})),
+        _toretar_layer(2, 16, 8, 24, 48, 0.3, 500.0, 8, None),
+        _toretar_layer(5, 8, 4, 8, 24, 0.5, 100000.0, 4, _toretar_moe(3, 1, 24, 2.5, None)),
+    ],
+}
+
+# Toretar with sizes the tensor-core kernels take (rows of 16-byte multiples, rank a multiple of
+# 16): one head in a layer, all experts chosen in another, a shared expert wider than the routed.
+TORETAR_B = {
+    "architecture": "Toretar", "vocab": 520, "width": 128, "norm": {"eps": 1e-6},
+    "layers": [
+        _toretar_layer(4, 32, 16, 48, 64, 0.144, 250000.0, 16, _toretar_moe(6, 3, 64, 1.0, {"ff": 96, "limit": 2.0})),
+        _toretar_layer(1, 64, 32, 64, 96, 0.1, 10000.0, 32, _toretar_moe(2, 2, 32, 1.2, {"ff": 32, "limit": 0.9})),
+        _toretar_layer(9, 16, 16, 32, 128, 0.177, 1000000.0, 16, _toretar_moe(8, 2, 48, 3.0, {"ff": 64, "limit": 1.0})),
+    ],
+}
