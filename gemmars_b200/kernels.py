@@ -885,20 +885,78 @@ def rope_pairs(x, tok_pos, inv_freq, rot):
              _stream()), "rope_pairs", "elementwise", 2 * t * heads * rot * x.element_size())
 
 
+def latent_attention_mma_usable(dtype, rank: int, rd: int, page_size: int) -> bool:
+    """Whether the tensor-core kernel takes these sizes: bfloat16, the latent and the rotated part
+    multiples of 16 (the latent a multiple of 32 above 128 and of 64 above 256, up to 512: its
+    columns are dealt to 2 or 4 warps), pages of 64."""
+    if dtype != torch.bfloat16 or page_size != 64 or rank % 16 or rd % 16 or not 16 <= rank <= 512:
+        return False
+    return rank % (16 if rank <= 128 else (32 if rank <= 256 else 64)) == 0
+
+
+_latent_scratch = {}
+
+
+def latent_attention_mma(qa, out, heads, rank, rd, cache, page_table, page_size, cu_seqlens, seq_start, seq_slot,
+                         max_new: int, window=None, ksplits: int = 1, cache_bytes: int = 0):
+    """bfloat16 latent attention on the tensor cores (mma.sync) for packed sequences that bring any
+    number of tokens each; with ``ksplits`` > 1 the keys of a tile of rows are dealt to that many
+    CTAs and a second kernel adds their parts."""
+    _cuda(qa, out, cache, page_table, cu_seqlens, seq_start, seq_slot)
+    if not latent_attention_mma_usable(qa.dtype, rank, rd, page_size):
+        raise KernelError(f"latent_attention_mma: latent {rank} + {rd}, pages of {page_size} or {qa.dtype} not supported")
+    assert qa.stride(-1) == 1 and out.stride(-1) == 1 and out.dtype == cache.dtype == torch.bfloat16 and cache.is_contiguous()
+    assert qa.shape[1] == heads * (rank + rd) and out.shape[1] == heads * rank and cache.shape[-1] == rank + rd
+    ntok = qa.shape[0]
+    defines = (("GB_LATENT_RANK", rank), ("GB_LATENT_ROT", rd))
+    part = None
+    if ksplits > 1:
+        need = ntok * heads * ksplits * (2 + rank)
+        part = _latent_scratch.get(qa.device.index)
+        if part is None or part.numel() < need:
+            if part is not None:
+                _outgrown.append(part)        # a captured step may still point at it: never freed
+            part = _latent_scratch[qa.device.index] = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=qa.device)
+    f = _fn("latent_attention_mma", "gb_latent_attention_mma",
+            [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p], defines=defines)
+    _check(f(qa.data_ptr(), qa.stride(0), out.data_ptr(), out.stride(0), _ptr(part), cache.data_ptr(), page_table.data_ptr(),
+             page_table.shape[1], page_size, cu_seqlens.data_ptr(), seq_start.data_ptr(), seq_slot.data_ptr(),
+             seq_slot.numel(), ntok, heads, rank, rd, max_new * heads, window or 0, ksplits, _stream()),
+           "latent_attention_mma", "attention", _nbytes(qa, out) + cache_bytes)
+    if ksplits > 1:
+        count_launches(1)   # the merge kernel
+
+
+def latent_decode_splits(n_seqs: int, heads: int) -> int:
+    """CTAs along the keys for each sequence of a decode step: about one CTA per SM in all."""
+    tiles = n_seqs * -(-heads // 64)
+    return max(1, min(32, sm_count() // max(tiles, 1)))
+
+
 def latent_attention(ctx, qa, out, heads, rank, rd, cache, page_table, page_size, window=None):
     """Latent attention of the step's queries over the cache; picks the kernel for the precision
-    and the sizes.  float32 always takes the plain kernel."""
+    and the sizes.  float32 always takes the plain kernel, whose arithmetic for a position does not
+    depend on the batch; so do sizes the tensor-core kernel does not take."""
     cached = 0
     if _profile["on"] and ctx.host is not None:
         per_pos = (rank + rd) * cache.element_size()
         for start, n in zip(ctx.host["seq_start"], ctx.host["seq_len"]):
             cached += per_pos * (min(start + n, window + n - 1) if window else start + n)
+    if latent_attention_mma_usable(qa.dtype, rank, rd, page_size) and qa.stride(0) % 8 == 0:
+        ksplits = latent_decode_splits(ctx.n_seqs, heads) if ctx.max_new <= 1 else 1
+        latent_attention_mma(qa, out, heads, rank, rd, cache, page_table, page_size, ctx.cu_seqlens, ctx.seq_start,
+                             ctx.seq_slot, ctx.max_new, window, ksplits, cache_bytes=cached)
+        return
     latent_attention_ref(qa, out, heads, rank, rd, cache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
                          window, cache_bytes=cached)
 
 
 def latent_attention_units(compute: str, rank: int, rd: int):
-    return [("latent_attention", ())]
+    units = [("latent_attention", ())]
+    if compute != "float32" and latent_attention_mma_usable(torch.bfloat16, rank, rd, 64):
+        units.append(("latent_attention_mma", (("GB_LATENT_RANK", rank), ("GB_LATENT_ROT", rd))))
+    return units
 
 
 # --------------------------------------------------------------------------- routed feed-forward
