@@ -2,6 +2,7 @@
 """Decode and prefill throughput of Qwen3-shaped models with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference] [--config 8b|4b|32b]
+    python bench.py --compare toretar [--sizes small,lite,mid] [--batch 8] [--context 4096]
 
 ``--config 8b`` (the default) is the headline benchmark.  A step is one decode step of a batch
 of 8 sequences at a context of 8,192 tokens.  One JSON line is printed: ``value`` = decoded
@@ -101,7 +102,12 @@ class ClockSampler:
 
 def kv_bytes_per_token(runner):
     """Bytes of keys and values one cached position takes over all layers (groups that keep all keys)."""
-    return sum(2 * g.n_layers * g.need.num_kv_heads * g.need.head_dim * g.k.element_size() for g in runner.cache.kv_groups)
+    return sum(g.n_layers * g.need.num_kv_heads * (g.need.head_dim + _value_dim(g)) * g.k.element_size()
+               for g in runner.cache.kv_groups)
+
+
+def _value_dim(group):
+    return group.need.head_dim if group.need.value_dim is None else group.need.value_dim
 
 
 def decode_bytes(model, runner, lengths):
@@ -109,7 +115,7 @@ def decode_bytes(model, runner, lengths):
     the live sequences."""
     kv = 0
     for g in runner.cache.kv_groups:
-        per_token = 2 * g.n_layers * g.need.num_kv_heads * g.need.head_dim * g.k.element_size()
+        per_token = g.n_layers * g.need.num_kv_heads * (g.need.head_dim + _value_dim(g)) * g.k.element_size()
         for n in lengths:
             kv += per_token * (min(n, g.need.window) if g.need.window else n)
     return model.weight_bytes() + kv
@@ -121,6 +127,22 @@ def prefill_flops(cfg, t):
     per_token = 2 * (h * (nh + 2 * nkv) * hd + nh * hd * h + 3 * h * i)
     attn = 4 * nh * hd * (t * (t + 1) // 2)           # QK^T and PV over the causal half
     return cfg["num_hidden_layers"] * (per_token * t + attn) + 2 * h * v  # logits of the last row only
+
+
+def toretar_prefill_flops(cfg, t):
+    """Floating-point operations of a prompt of ``t`` tokens as the engine computes it (both
+    expansions on the query side: attention runs over rows of kv_rank + rot_dim)."""
+    w, total = cfg["width"], 0
+    for layer in cfg["layers"]:
+        m, mlp = layer["mixer"], layer["mlp"]
+        nh, dim, rd, vd, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+        per_token = 2 * (w * (nh * (dim + rd) + r + rd + nh) + nh * dim * r + nh * r * vd + nh * vd * w)
+        if mlp is not None:
+            per_token += 2 * w * mlp["router"]["experts"] + 6 * w * mlp["router"]["top"] * mlp["expert"]["ff"]
+            if mlp.get("shared"):
+                per_token += 6 * w * mlp["shared"]["ff"]
+        total += per_token * t + 2 * nh * (2 * r + rd) * (t * (t + 1) // 2)
+    return total + 2 * w * cfg["vocab"]
 
 
 def fill_cache(runner, slots, length, real, vocab, gen):
@@ -196,7 +218,8 @@ def time_prefill(eng, cfg, tokens, tflops, tflops_sustained):
     import torch
     from gemmars_b200.engine.step import StepItem
     runner = eng.runner
-    toks = torch.randint(0, cfg["vocab_size"], (tokens,), generator=torch.Generator().manual_seed(3)).tolist()
+    vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
+    toks = torch.randint(0, vocab, (tokens,), generator=torch.Generator().manual_seed(3)).tolist()
     pre_ms = []
     for it in range(10):
         s = runner.open()
@@ -210,7 +233,8 @@ def time_prefill(eng, cfg, tokens, tflops, tflops_sustained):
             pre_ms.append(e0.elapsed_time(e1))
         runner.close(s)
     pre = statistics.median(pre_ms)
-    frac = prefill_flops(cfg, tokens) / (pre / 1e3) / (tflops * 1e12)
+    flops = toretar_prefill_flops(cfg, tokens) if "layers" in cfg else prefill_flops(cfg, tokens)
+    frac = flops / (pre / 1e3) / (tflops * 1e12)
     return {"value": round(tokens / (pre / 1e3), 1), "tokens": tokens, "ms": round(pre, 3), "frac": round(frac, 4),
             # a prompt is tens of milliseconds of products under the power cap: also against the sustained rate
             "frac_sustained": round(frac * tflops / tflops_sustained, 4)}
@@ -355,6 +379,73 @@ def run_32b(args, name, cfg, layers_full):
     }
 
 
+def kernel_table(eng, tokens, batch, context):
+    """Per kernel, without captured steps: calls, microseconds a call and the bytes the launch said
+    it moves, for one prompt of ``tokens`` tokens and for one decode step of ``batch`` sequences at
+    ``context`` cached tokens."""
+    import torch
+    from gemmars_b200 import kernels
+    from gemmars_b200.engine.step import StepItem
+    runner = eng.runner
+    was, runner.use_graphs = runner.use_graphs, False
+    out = {}
+    try:
+        toks = torch.randint(0, eng.model.plan.vocab_size, (tokens,), generator=torch.Generator().manual_seed(5)).tolist()
+        for phase in ("prompt", "decode"):
+            if phase == "prompt":
+                slots = [runner.open()]
+                items = [StepItem(slots[0], toks, [tokens - 1])]
+                warm = [StepItem(slots[0], toks[:tokens], [])]
+            else:
+                slots = [runner.open() for _ in range(batch)]
+                synthetic_fill(runner, slots, context - 2)
+                items = [StepItem(s, [1], [0]) for s in slots]
+                warm = items
+            if phase == "prompt":       # a warm-up prompt in a slot of its own
+                s2 = runner.open()
+                runner.step([StepItem(s2, toks, [tokens - 1])])
+                runner.close(s2)
+            else:
+                runner.step(warm)
+            torch.cuda.synchronize()
+            kernels.profile_start()
+            runner.step(items)
+            totals = kernels.profile_totals()
+            out[phase] = {name: {"calls": c, "us_per_call": round(ms * 1e3 / c, 2), "mb_per_call": round(nb / c / 1e6, 3)}
+                          for name, (c, ms, nb) in sorted(totals["kernels"].items(), key=lambda kv: -kv[1][1])}
+            for s in slots:
+                runner.close(s)
+    finally:
+        runner.use_graphs = was
+    return out
+
+
+def run_compare(args):
+    """Prompt and decode throughput of Toretar-shaped models beside Qwen3-shaped models of the same
+    width, depth and per-token feed-forward size, with a table of each one's kernels."""
+    from gemmars_b200.tuning import PAIRS
+    hbm_gbs, tflops, tflops_sustained, peak_src = peaks()
+    sizes = [s for s in args.sizes.split(",") if s]
+    out = {}
+    for size in sizes:
+        out[size] = {}
+        for arch, cfg in zip(("toretar", "qwen3"), PAIRS[size]):
+            eng = make_engine(cfg, args.batch, args.batch * (args.context + 64) + PREFILL_TOKENS + 64, args.options)
+            rec = {"prefill": time_prefill(eng, cfg, PREFILL_TOKENS, tflops, tflops_sustained),
+                   "decode": time_decode(eng, args.batch, args.context, args.steps, max(3, args.warmup), False, hbm_gbs)}
+            if not args.no_points:
+                rec["kernels"] = kernel_table(eng, PREFILL_TOKENS, args.batch, args.context)
+            out[size][arch] = rec
+            del eng
+            import gc
+            import torch
+            gc.collect()
+            torch.cuda.empty_cache()
+    return {"compare": "toretar beside qwen3", "sizes": out, "batch": args.batch, "context": args.context,
+            "prefill_tokens": PREFILL_TOKENS, "peaks": f"{hbm_gbs:.0f} GB/s, {tflops:.0f} TFLOP/s ({peak_src})",
+            "dtype": "bf16", "data": "synthetic: random weights, random token ids, cache filled with random rows"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -371,6 +462,9 @@ def main():
     ap.add_argument("--e2e-tokens", type=int, default=E2E_TOKENS,
                     help="tokens a sequence generates in the end-to-end run (fewer for runs under a profiler)")
     ap.add_argument("--options", default="", help='further engine options, "key=value;key=value"')
+    ap.add_argument("--compare", choices=["toretar"], default=None,
+                    help="instead of the headline: Toretar-shaped models beside Qwen3-shaped ones of equal size")
+    ap.add_argument("--sizes", default="small,lite,mid", help="with --compare: which pairs of tuning.PAIRS")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -380,6 +474,9 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported", flush=True)
         return 2
+    if args.compare:
+        print(json.dumps(run_compare(args)), flush=True)
+        return 0
     name, cfg = CONFIGS[args.config]
     layers_full = cfg["num_hidden_layers"]
     cfg = dict(cfg, num_hidden_layers=args.layers or layers_full)

@@ -91,7 +91,7 @@ class profile_category:
 
 
 def profile_totals() -> dict:
-    """{"kernels": {name: [calls, ms]}, "categories": {name: [calls, ms, bytes]}} since
+    """{"kernels": {name: [calls, ms, bytes]}, "categories": {name: [calls, ms, bytes]}} since
     profile_start; stops collecting.  Synchronizes."""
     _profile["on"] = False
     torch.cuda.synchronize()
@@ -99,9 +99,10 @@ def profile_totals() -> dict:
     per_kernel, per_cat = {}, {}
     for (_, _, _, a), (name, cat, nbytes, b) in zip(ev, ev[1:]):
         ms = a.elapsed_time(b)
-        t = per_kernel.setdefault(name, [0, 0.0])
+        t = per_kernel.setdefault(name, [0, 0.0, 0])
         t[0] += 1
         t[1] += ms
+        t[2] += nbytes
         c = per_cat.setdefault(cat, [0, 0.0, 0])
         c[0] += 1
         c[1] += ms
@@ -127,7 +128,7 @@ def profile_report(tokens: int = 1, totals: Optional[dict] = None) -> str:
         lines.append(f"{str(cat):14s} {ms / tokens:9.4f} {calls / tokens:10.2f} {ms * 1e3 / calls:9.1f} "
                      f"{nbytes / tokens / 1e6:10.4f} {nbytes / max(ms, 1e-9) / 1e6:8.1f} {100 * ms / whole:6.1f}%")
     lines.append(f"{'kernel':28s} {'ms/tok':>9s} {'calls/tok':>10s} {'us/call':>9s} {'share':>7s}")
-    for name, (calls, ms) in sorted(totals["kernels"].items(), key=lambda kv: -kv[1][1]):
+    for name, (calls, ms, _) in sorted(totals["kernels"].items(), key=lambda kv: -kv[1][1]):
         lines.append(f"{name:28s} {ms / tokens:9.4f} {calls / tokens:10.2f} {ms * 1e3 / calls:9.1f} {100 * ms / whole:6.1f}%")
     lines.append(f"{'total':28s} {whole / tokens:9.4f}")
     return "\n".join(lines)
@@ -848,12 +849,40 @@ def heads_gemm(x, w, y, heads, scale=None):
     assert x.stride(2) == 1 and y.stride(2) == 1 and x.dtype == w.dtype == y.dtype
     if scale is not None:
         assert scale.dtype == torch.float32 and scale.shape == (t, heads) and scale.is_contiguous()
+    if (x.dtype == torch.bfloat16 and k % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0
+            and x.data_ptr() % 16 == 0 and t >= HEADS_GEMM_TC_MIN_TOKENS):
+        grouped_gemm(x, x.stride(0), x.stride(1), None, 1, w, n * k, y, y.stride(0), y.stride(1), scale, None, heads, 1,
+                     None, heads, t, t, n, k, what="heads_gemm_tc", nbytes=_nbytes(w) + t * heads * (n + k) * 2)
+        return
     f = _fn("latent_attention", "gb_heads_gemm",
             [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_int,
              c_int, c_int, c_void_p])
     _check(f(x.data_ptr(), x.stride(0), x.stride(1), w.data_ptr(), y.data_ptr(), y.stride(0), y.stride(1), _ptr(scale),
              dtype_code(x.dtype), t, heads, n, k, _stream()), "heads_gemm", "matmul",
            _nbytes(w) + t * heads * (n + k) * x.element_size())
+
+
+# below this many tokens the per-head products are a matrix-vector job: the FFMA kernel's 64-row
+# tiles read the weights once either way, and a 128-row tensor-core tile would be nearly empty
+HEADS_GEMM_TC_MIN_TOKENS = 17
+
+
+def grouped_gemm(a, lda, a_gstride, a_rows, a_div, w, w_gstride, c, ldc, c_gstride, scale, scale_rows, s_rstride, s_gstride,
+                 offsets, groups, rows, max_rows, n, k, gated=False, limit=0.0, alpha=0.0, shift=0.0, what="grouped_gemm",
+                 nbytes=0):
+    """Many bfloat16 products C_g = A_g W_g^T of unequal row counts in one tensor-core launch (see
+    csrc/grouped_gemm.cu): group g's rows are offsets[g]..offsets[g+1] (None: ``rows`` each), an A
+    row is a_rows[i] // a_div (None: i), C is bfloat16 or float32 by its dtype; ``gated``: W_g stacks
+    gate rows over up rows and C = min(g, limit) * sigmoid(alpha g) * (clamp(u) + shift)."""
+    _cuda(a, w, c, scale, scale_rows, offsets, a_rows)
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and c.dtype in (torch.bfloat16, torch.float32)
+    f = _fn("grouped_gemm", "gb_grouped_gemm",
+            [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_longlong,
+             c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+             c_float, c_float, c_void_p])
+    _check(f(a.data_ptr(), lda, a_gstride, _ptr(a_rows), a_div, w.data_ptr(), w_gstride, c.data_ptr(), ldc, c_gstride,
+             _ptr(scale), _ptr(scale_rows), s_rstride, s_gstride, _ptr(offsets), groups, rows, max_rows, n, k,
+             1 if gated else 0, 1 if c.dtype == torch.float32 else 0, limit, alpha, shift, _stream()), what, "matmul", nbytes)
 
 
 def latent_attention_ref(qa, out, heads, rank, rd, cache, page_table, page_size, tok_pos, tok_seq, seq_slot, window=None,
@@ -1010,6 +1039,54 @@ def moe_experts(h, idx, wts, sg, w_gate_up, w_down, shared_gate_up, shared_down,
     _check(f(y.data_ptr(), dtype_code(h.dtype), idx.data_ptr(), wts.data_ptr(), _ptr(sg), w_down.data_ptr(),
              _ptr(shared_down), residual.data_ptr(), residual.stride(0), t, width, ff, ffs, top, _stream()), "moe_down",
            "matmul", _nbytes(y) + 2 * t * width * 4 + t * slots * ff * width * h.element_size())
+
+
+MOE_GROUPED_MIN_TOKENS = 16
+
+
+def moe_grouped_usable(h, w_gate_up, w_down) -> bool:
+    """Whether a step's experts run as grouped tensor-core products: bfloat16, enough tokens that
+    experts are shared between them, rows that cp.async can bring in 16-byte pieces."""
+    return (h.dtype == torch.bfloat16 and h.shape[0] >= MOE_GROUPED_MIN_TOKENS and h.shape[1] % 8 == 0
+            and w_down.shape[2] % 8 == 0 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0)
+
+
+def moe_experts_grouped(h, idx, wts, sg, w_gate_up, w_down, shared_gate_up, shared_down, residual, limit, shared_limit,
+                        alpha, shift):
+    """As moe_experts for a step of many tokens: the (token, slot) entries are ordered by expert on the
+    device, each expert's rows run as one product of a grouped tensor-core launch (gate/up with the
+    activation, then down scaled by the routing weights), a token's rows are added into the residual
+    in slot order, and the shared expert runs as dense products over all tokens."""
+    _cuda(h, idx, wts, sg, w_gate_up, w_down, shared_gate_up, shared_down, residual)
+    t, width = h.shape
+    e, ff2, _ = w_gate_up.shape
+    ff, top = ff2 // 2, idx.shape[1]
+    entries = t * top
+    assert residual.dtype == torch.float32 and residual.stride(1) == 1 and idx.is_contiguous() and wts.is_contiguous()
+    meta = torch.empty(e + 1 + 2 * entries, dtype=torch.int32, device=h.device)
+    offsets, perm, place = meta[:e + 1], meta[e + 1:e + 1 + entries], meta[e + 1 + entries:]
+    f = _fn("grouped_gemm", "gb_moe_sort", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(idx.data_ptr(), entries, e, offsets.data_ptr(), perm.data_ptr(), place.data_ptr(), _stream()), "moe_sort",
+           "elementwise", 3 * entries * 4)
+    y = torch.empty((entries, ff), dtype=torch.bfloat16, device=h.device)
+    grouped_gemm(h, h.stride(0), 0, perm, top, w_gate_up, ff2 * width, y, ff, 0, None, None, 0, 0, offsets, e, 0, entries,
+                 ff, width, gated=True, limit=limit, alpha=alpha, shift=shift, what="moe_gate_up_tc",
+                 nbytes=_nbytes(w_gate_up, y) + entries * width * 2)
+    rows = torch.empty((entries, width), dtype=torch.float32, device=h.device)
+    grouped_gemm(y, ff, 0, None, 1, w_down, width * ff, rows, width, 0, wts.view(-1), perm, 1, 0, offsets, e, 0, entries,
+                 width, ff, what="moe_down_tc", nbytes=_nbytes(w_down, y, rows))
+    f = _fn("grouped_gemm", "gb_moe_combine", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p])
+    _check(f(rows.data_ptr(), place.data_ptr(), residual.data_ptr(), residual.stride(0), t, width, top, _stream()),
+           "moe_combine", "elementwise", _nbytes(rows) + 2 * t * width * 4)
+    if shared_down is not None:
+        ffs = shared_down.shape[1]
+        gu = torch.empty((t, 2 * ffs), dtype=torch.bfloat16, device=h.device)
+        gemm(h, shared_gate_up, gu)
+        ys = torch.empty((t, ffs), dtype=torch.bfloat16, device=h.device)
+        f = _fn("grouped_gemm", "gb_gated_act", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_void_p])
+        _check(f(gu.data_ptr(), ys.data_ptr(), _ptr(sg), t, ffs, shared_limit, alpha, shift, _stream()), "gated_act",
+               "elementwise", _nbytes(gu, ys))
+        gemm(ys, shared_down, residual, accumulate=True)
 
 
 # --------------------------------------------------------------------------- sampling

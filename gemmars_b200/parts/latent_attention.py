@@ -81,7 +81,8 @@ class LatentAttention(Part):
         self.norm_w = t["dkv_norm"].contiguous()
 
     def kernel_units(self):
-        return (kernels.gemm_units(self.compute) + kernels.latent_attention_units(self.compute, self.rank, self.rot_dim))
+        units = kernels.gemm_units(self.compute) + kernels.latent_attention_units(self.compute, self.rank, self.rot_dim)
+        return units + ([("grouped_gemm", ())] if self.compute != "float32" else [])
 
     def cache_needs(self):
         return [KVNeed(1, self.rank + self.rot_dim, self.window, value_dim=0)]

@@ -74,7 +74,9 @@ class RoutedExperts(Part):
                 self.shared_gate = None
 
     def kernel_units(self):
-        return [("moe", ())]
+        if self.compute == "float32":
+            return [("moe", ())]
+        return [("moe", ()), ("grouped_gemm", ())] + kernels.gemm_units(self.compute)
 
     def weight_bytes(self):
         """What a decode step of one token reads: the router, ``top`` experts, the shared expert."""
@@ -87,7 +89,8 @@ class RoutedExperts(Part):
         idx, wts, sg = kernels.moe_route(h, self.router, self.bias, self.shared_gate, self.top)
         if self.shared_ff and sg is None:
             sg = torch.ones((h.shape[0],), dtype=torch.float32, device=h.device)
-        kernels.moe_experts(h, idx, wts, sg, self.gate_up, self.down, self.shared_gate_up, self.shared_down, residual,
+        run = kernels.moe_experts_grouped if kernels.moe_grouped_usable(h, self.gate_up, self.down) else kernels.moe_experts
+        run(h, idx, wts, sg, self.gate_up, self.down, self.shared_gate_up, self.shared_down, residual,
                             self.limit, self.shared_limit, self.alpha, self.shift)
 
 

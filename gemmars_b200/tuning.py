@@ -37,6 +37,40 @@ SHAPES = {
 }
 
 
+def toretar_shape(layers, width, heads, dim, rot_dim, vdim, rank, experts, top, ff, shared_ff, vocab=102400):
+    """A Toretar config.json object of the given layer sizes (every layer alike)."""
+    layer = {"type": "latent_attention",
+             "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank,
+                       "scale": (dim + rot_dim) ** -0.5, "rot": {"base": 10000.0, "dims": rot_dim}},
+             "mlp": {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff, "limit": 7.0},
+                     "shared": {"ff": shared_ff, "limit": 7.0}}}
+    return {"architecture": "Toretar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [layer] * layers}
+
+
+def _pair(layers, width, heads, dim, rot_dim, vdim, rank, experts, top, ff, shared_ff, qwen_heads, qwen_kv):
+    """A Toretar shape and the Qwen3 shape beside it: the same width, layers and vocabulary, heads
+    of 128, and a feed-forward as wide as what one Toretar token runs (top experts + the shared one)."""
+    q = qwen3_shape(layers, width, qwen_heads, qwen_kv, top * ff + shared_ff, False)
+    q["vocab_size"] = 102400
+    return toretar_shape(layers, width, heads, dim, rot_dim, vdim, rank, experts, top, ff, shared_ff), q
+
+
+# Layer sizes in the range of released latent-attention mixture-of-experts models, four layers each
+PAIRS = {
+    "small": _pair(4, 1024, 8, 64, 32, 64, 256, 16, 2, 512, 1024, 8, 4),
+    "lite": _pair(4, 2048, 16, 128, 64, 128, 512, 64, 6, 1408, 2816, 16, 8),
+    "mid": _pair(4, 4096, 32, 128, 64, 128, 512, 32, 4, 2048, 4096, 32, 8),
+}
+
+
+# the same pairs by name, for ``timeline --shape toretar-lite`` and ``--shape beside-lite``
+PAIR_SHAPES = {}
+for _name, (_t, _q) in PAIRS.items():
+    PAIR_SHAPES[f"toretar-{_name}"] = (f"Toretar shape '{_name}'", _t)
+    PAIR_SHAPES[f"beside-{_name}"] = (f"Qwen3 shape beside Toretar '{_name}'", _q)
+
+
 def random_engine(cfg, max_batch, cache_tokens, options=""):
     """An engine over random weights of ``cfg`` made on the device; the tensors are taken out of
     their dict as they are bound, so that a model of 65 GB and its stacked q/k/v and gate/up copies
@@ -130,10 +164,15 @@ def timeline(shape, batch, context, layers, prompt, temperature, out=sys.stdout)
     from torch.profiler import ProfilerActivity, profile
     from .engine.step import StepItem
     from .sampling.sampler import BatchSampler, SamplingParams
-    label, cfg = SHAPES[shape]
-    cfg = dict(cfg, num_hidden_layers=layers or cfg["num_hidden_layers"])
+    label, cfg = {**SHAPES, **PAIR_SHAPES}[shape]
+    if "layers" in cfg:
+        cfg = dict(cfg, layers=cfg["layers"][:layers or len(cfg["layers"])])
+        n_layers, vocab = len(cfg["layers"]), cfg["vocab"]
+    else:
+        cfg = dict(cfg, num_hidden_layers=layers or cfg["num_hidden_layers"])
+        n_layers, vocab = cfg["num_hidden_layers"], cfg["vocab_size"]
     eng = random_engine(cfg, max(batch, 1), max(batch, 1) * (max(context, prompt) + 128))
-    runner, vocab = eng.runner, cfg["vocab_size"]
+    runner = eng.runner
     if prompt:
         toks = torch.randint(0, vocab, (prompt,), generator=torch.Generator().manual_seed(3)).tolist()
 
@@ -167,7 +206,7 @@ def timeline(shape, batch, context, layers, prompt, temperature, out=sys.stdout)
         step()
     e1.record()
     torch.cuda.synchronize()
-    print(f"{label}, {cfg['num_hidden_layers']} layers, {what}: {e0.elapsed_time(e1) / 8 * 1e3:.1f} us a step "
+    print(f"{label}, {n_layers} layers, {what}: {e0.elapsed_time(e1) / 8 * 1e3:.1f} us a step "
           "(CUDA events, host turnaround included)", file=out)
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         for _ in range(3):
@@ -207,7 +246,7 @@ def main(argv=None) -> int:
     p.add_argument("--shapes", default="4b,8b,32b")
     p.add_argument("--tokens", default="1,8,16,32,64")
     t = sub.add_parser("timeline", help="the kernels of one replayed decode step or one prompt step")
-    t.add_argument("--shape", default="8b", choices=sorted(SHAPES))
+    t.add_argument("--shape", default="8b", choices=sorted(SHAPES) + sorted(PAIR_SHAPES))
     t.add_argument("--batch", type=int, default=8)
     t.add_argument("--context", type=int, default=8192)
     t.add_argument("--layers", type=int, default=6, help="layers of the model that is built (0: all)")
