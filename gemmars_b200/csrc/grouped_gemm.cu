@@ -11,14 +11,16 @@
 //    A and C rows are a token's slice of a wider row, with an optional scale per (token, head).
 //
 // A CTA of 8 warps computes a tile of 128 rows x 128 columns (mma.sync m16n8k16, float32
-// accumulation), operands staged in shared memory by cp.async three blocks of 32 deep.  A CTA
+// accumulation), operands staged in shared memory by cp.async three blocks of 64 deep.  A CTA
 // finds its group and row tile by walking the groups' offsets, so nothing comes back to the host
 // and the launches can be captured.
 #include "mma.cuh"
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3, LDS = BK + 8;
+constexpr int BM = 128, BN = 128, BK = 64, STAGES = 3, LDS = BK + 8;
+constexpr int CPR = BK / 8;          // 16-byte pieces of a row of a block
+constexpr int RPT = BM * CPR / 256;  // rows a thread brings in
 enum { MODE_PLAIN = 0, MODE_GATED = 1 };
 
 struct GroupedArgs {
@@ -43,8 +45,11 @@ __device__ __forceinline__ void ldsm4(uint32_t* r, const void* p) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
 
+__device__ __forceinline__ void store2(float* p, float x, float y) { *(float2*)p = make_float2(x, y); }
+__device__ __forceinline__ void store2(bf16* p, float x, float y) { *(uint32_t*)p = pack_bf16(x, y); }
+
 template <int MODE, typename TO>
-__global__ void __launch_bounds__(256) grouped_gemm_kernel(GroupedArgs p) {
+__global__ void __launch_bounds__(256, 2) grouped_gemm_kernel(GroupedArgs p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_release_next();
   pdl_wait_prior();
@@ -71,14 +76,14 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(GroupedArgs p) {
   const int n0 = blockIdx.y * (MODE == MODE_GATED ? BN / 2 : BN);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wm = warp >> 2, wn = warp & 3;             // 2 x 4 warps, 64 rows x 32 columns each
-  // ---- the two A rows and two W rows this thread brings in, every block of K
-  const int ch = tid & 3;
-  const bf16* a_src[2];
-  const bf16* w_src[2];
-  bool a_ok[2], w_ok[2];
+  // ---- the A rows and W rows this thread brings in, every block of K
+  const int ch = tid % CPR;
+  const bf16* a_src[RPT];
+  const bf16* w_src[RPT];
+  bool a_ok[RPT], w_ok[RPT];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int r = (tid >> 2) + 64 * i;
+  for (int i = 0; i < RPT; ++i) {
+    const int r = tid / CPR + (256 / CPR) * i;
     const int lr = mt * BM + r;
     a_ok[i] = lr < cnt;
     long long arow = 0;
@@ -99,8 +104,8 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(GroupedArgs p) {
   auto load = [&](int kb, int stage) {
     const bool k_ok = kb * BK + ch * 8 < p.K;          // K is a multiple of 8: a piece is whole or absent
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int r = (tid >> 2) + 64 * i;
+    for (int i = 0; i < RPT; ++i) {
+      const int r = tid / CPR + (256 / CPR) * i;
       cp_async16_or_zero(As + ((size_t)stage * BM + r) * LDS + ch * 8, a_src[i] + (size_t)kb * BK, a_ok[i] && k_ok);
       cp_async16_or_zero(Ws + ((size_t)stage * BN + r) * LDS + ch * 8, w_src[i] + (size_t)kb * BK, w_ok[i] && k_ok);
     }
@@ -168,12 +173,16 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(GroupedArgs p) {
           }
       } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = n0 + wn * 32 + j * 8 + 2 * cq + e;
-            if (col < p.N) dst[col] = from_f32<TO>(acc[i][j][2 * half + e] * sc);
+        for (int j = 0; j < 4; ++j) {
+          const int col = n0 + wn * 32 + j * 8 + 2 * cq;
+          const float x = acc[i][j][2 * half] * sc, y = acc[i][j][2 * half + 1] * sc;
+          if (col + 1 < p.N && ((uintptr_t)(dst + col) & (2 * sizeof(TO) - 1)) == 0) {
+            store2(dst + col, x, y);
+          } else {
+            if (col < p.N) dst[col] = from_f32<TO>(x);
+            if (col + 1 < p.N) dst[col + 1] = from_f32<TO>(y);
           }
+        }
       }
     }
 }

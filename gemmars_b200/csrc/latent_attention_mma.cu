@@ -10,11 +10,14 @@
 //   P = softmax      online, float32, log2 units, each row masked at its own position (and window)
 //   O += P V         V = the first RANK columns of the same key tile (ldmatrix.trans)
 //
-// A group of 16 rows is worked by NSPLIT warps: each scores a share of the tile's keys, the
-// scores meet in shared memory, and each warp then owns RANK / NSPLIT of the output's columns,
-// so that a wide latent does not have to fit one warp's registers.  Key tiles arrive by cp.async,
-// one tile ahead.  With `ksplits` > 1 (decoding: few rows, many keys) the keys of a tile of rows
-// are dealt to ksplits CTAs, which leave (m, l, o) parts that a second kernel adds in split
+// A group of 16 rows is worked by NSPLIT warps.  Each keeps its share of the queries' columns in
+// registers for the whole kernel and scores every key of a tile over that share alone, so a key
+// tile is read from shared memory once per group, not once per warp; the partial scores meet in
+// shared memory and are added in warp order.  Each warp then owns RANK / NSPLIT of the output's
+// columns, so that a wide latent does not have to fit one warp's registers.  Key tiles arrive by
+// cp.async, one tile ahead; the queries pass through the same buffers before the first tile.
+// With `ksplits` > 1 (decoding: few rows, many keys) the keys of a tile of rows are dealt to
+// ksplits CTAs, which leave (m, l, o) parts that a second kernel adds in split
 // order: the same bits every run.
 #include "mma.cuh"
 
@@ -31,15 +34,16 @@ constexpr int RANK = GB_LATENT_RANK, ROT = GB_LATENT_ROT, KD = RANK + ROT;
 static_assert(RANK % 16 == 0 && ROT % 16 == 0 && RANK >= 16, "latent and rotated widths must be multiples of 16");
 constexpr int NSPLIT = RANK <= 128 ? 1 : (RANK <= 256 ? 2 : 4);
 static_assert(RANK % (16 * NSPLIT) == 0, "the latent must divide into 16-column blocks per warp");
-constexpr int KEYS = KD <= 288 ? 64 : 32;
+constexpr int KEYS = 64;
 constexpr int LDS = KD + ((KD / 8) % 2 == 0 ? 8 : 0);   // row pitch in shared memory: an odd number of 16-byte units
 constexpr int NB = KEYS / 8;                             // blocks of 8 keys a tile
-constexpr int NBW = NB / NSPLIT;                         // blocks a warp scores
+constexpr int KSTEPS = KD / 16;                          // 16-column steps of a score
+constexpr int KSW = (KSTEPS + NSPLIT - 1) / NSPLIT;      // steps a warp owns
 constexpr int DW = RANK / NSPLIT;                        // output columns a warp owns
 constexpr int SXP = KEYS + 4;                            // pitch of the exchanged scores
-constexpr int MAX_GROUPS = 4;                            // groups of 16 rows a CTA at most
+constexpr int MAX_GROUPS = NSPLIT == 4 ? 2 : 4;          // groups of 16 rows a CTA at most (<= 2 * KEYS rows: the queries' staging)
 constexpr float LOG2E = 1.4426950408889634f;
-static_assert(NB % NSPLIT == 0, "key blocks must divide among the warps of a row group");
+static_assert(NB % 2 == 0 && MAX_GROUPS * 16 <= 2 * KEYS, "key blocks come in pairs; the queries are staged in the key buffers");
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -51,10 +55,6 @@ __device__ __forceinline__ void ldsm_x4(uint32_t* r, const void* p) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-__device__ __forceinline__ void ldsm_x2(uint32_t* r, const void* p) {
-  const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(s));
 }
 __device__ __forceinline__ void ldsm_x4_t(uint32_t* r, const void* p) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(p);
@@ -74,9 +74,9 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, long long ldq, bf16* __
   pdl_wait_prior();
   const int groups = blockDim.x / (32 * NSPLIT);
   const int tile_rows = groups * 16;
-  bf16* Qs = (bf16*)smem_raw;                         // [tile_rows][LDS]
-  bf16* Ks = Qs + (size_t)tile_rows * LDS;            // [2][KEYS][LDS]
-  float* Sx = (float*)(Ks + 2 * KEYS * LDS);          // [groups][16][SXP], only with NSPLIT > 1
+  bf16* Ks = (bf16*)smem_raw;                         // [2][KEYS][LDS]
+  bf16* Qs = Ks;                                      // [tile_rows][LDS], before the first key tile
+  float* Sx = (float*)(Ks + 2 * KEYS * LDS);          // [groups][NSPLIT][16][SXP], only with NSPLIT > 1
   // ---- which sequence and which tile of its rows
   int b = 0, tile = blockIdx.x, rows_b = 0;
   for (; b < n_seqs; ++b) {
@@ -124,6 +124,21 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, long long ldq, bf16* __
       cp_async16(dst + (size_t)r * LDS + ch * 8, src + (size_t)r * KD + ch * 8);
     }
   };
+  // ---- this warp's share of the queries' columns, into registers
+  cp_async_commit();
+  cp_async_wait_all();
+  __syncthreads();
+  uint32_t qf[KSW][4];
+  {
+    const bf16* q_lane = Qs + (size_t)(rg * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + 8 * (lane >> 4);
+#pragma unroll
+    for (int i = 0; i < KSW; ++i) {
+      const int ks = w * KSW + i;
+      if (ks < KSTEPS) ldsm_x4(qf[i], q_lane + ks * 16);
+      else qf[i][0] = qf[i][1] = qf[i][2] = qf[i][3] = 0;
+    }
+  }
+  __syncthreads();                                     // the buffers are free for keys
   if (my_begin < my_end) load_keys(my_begin, 0);
   cp_async_commit();
 
@@ -131,7 +146,6 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, long long ldq, bf16* __
   float o[DW / 8][4];
 #pragma unroll
   for (int d = 0; d < DW / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
-  const bf16* q_lane = Qs + (size_t)(rg * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + 8 * (lane >> 4);
 
   for (int t = my_begin; t < my_end; ++t) {
     const int stage = (t - my_begin) & 1;
@@ -140,40 +154,43 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, long long ldq, bf16* __
     if (t + 1 < my_end) load_keys(t + 1, stage ^ 1);
     cp_async_commit();
     const bf16* kt = Ks + (size_t)stage * KEYS * LDS;
-    // ---- scores of this warp's share of the keys
+    // ---- scores of all the tile's keys over this warp's share of the columns
     float s[NB][4];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
     {
-      float sp[NBW][4];
+      const bf16* k_lane = kt + (size_t)((lane & 7) + 8 * (lane >> 4)) * LDS + 8 * ((lane >> 3) & 1);
 #pragma unroll
-      for (int j = 0; j < NBW; ++j) sp[j][0] = sp[j][1] = sp[j][2] = sp[j][3] = 0.f;
-      const bf16* k_lane = kt + (size_t)(w * NBW * 8 + (lane & 7)) * LDS + 8 * ((lane >> 3) & 1);
-#pragma unroll 4
-      for (int ks = 0; ks < KD / 16; ++ks) {
-        uint32_t a[4];
-        ldsm_x4(a, q_lane + ks * 16);
+      for (int i = 0; i < KSW; ++i) {
+        const int ks = w * KSW + i;
+        if (ks < KSTEPS) {
 #pragma unroll
-        for (int j = 0; j < NBW; ++j) {
-          uint32_t kb[2];
-          ldsm_x2(kb, k_lane + (size_t)j * 8 * LDS + ks * 16);
-          mma16816(sp[j], a[0], a[1], a[2], a[3], kb[0], kb[1]);
+          for (int j = 0; j < NB; j += 2) {
+            uint32_t kb[4];                              // keys 8j..8j+7: regs 0, 1; keys 8j+8..8j+15: regs 2, 3
+            ldsm_x4(kb, k_lane + (size_t)j * 8 * LDS + ks * 16);
+            mma16816(s[j], qf[i][0], qf[i][1], qf[i][2], qf[i][3], kb[0], kb[1]);
+            mma16816(s[j + 1], qf[i][0], qf[i][1], qf[i][2], qf[i][3], kb[2], kb[3]);
+          }
         }
       }
-      if (NSPLIT == 1) {
+      if (NSPLIT > 1) {
+        float* sx = Sx + (size_t)rg * NSPLIT * 16 * SXP;
+        float* mine = sx + (size_t)w * 16 * SXP;
 #pragma unroll
-        for (int j = 0; j < NBW; ++j) { s[j][0] = sp[j][0]; s[j][1] = sp[j][1]; s[j][2] = sp[j][2]; s[j][3] = sp[j][3]; }
-      } else {
-        float* sx = Sx + (size_t)rg * 16 * SXP;
-#pragma unroll
-        for (int j = 0; j < NBW; ++j) {
-          const int col = (w * NBW + j) * 8 + 2 * c;
-          *(float2*)(sx + g * SXP + col) = make_float2(sp[j][0], sp[j][1]);
-          *(float2*)(sx + (g + 8) * SXP + col) = make_float2(sp[j][2], sp[j][3]);
+        for (int j = 0; j < NB; ++j) {
+          *(float2*)(mine + g * SXP + j * 8 + 2 * c) = make_float2(s[j][0], s[j][1]);
+          *(float2*)(mine + (g + 8) * SXP + j * 8 + 2 * c) = make_float2(s[j][2], s[j][3]);
         }
         __syncthreads();
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-          const float2 x = *(const float2*)(sx + g * SXP + j * 8 + 2 * c);
-          const float2 y = *(const float2*)(sx + (g + 8) * SXP + j * 8 + 2 * c);
+          float2 x = make_float2(0.f, 0.f), y = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int ww = 0; ww < NSPLIT; ++ww) {
+            const float2 a = *(const float2*)(sx + (size_t)ww * 16 * SXP + g * SXP + j * 8 + 2 * c);
+            const float2 bb = *(const float2*)(sx + (size_t)ww * 16 * SXP + (g + 8) * SXP + j * 8 + 2 * c);
+            x.x += a.x; x.y += a.y; y.x += bb.x; y.y += bb.y;
+          }
           s[j][0] = x.x; s[j][1] = x.y; s[j][2] = y.x; s[j][3] = y.y;
         }
       }
@@ -252,24 +269,30 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, long long ldq, bf16* __
 }
 
 // one block per (token, head): adds the splits' parts in split order
+constexpr int MAX_KSPLITS = 64;
+
 __global__ void __launch_bounds__(128) latent_attention_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out,
                                                                      long long ldo, int H, int ksplits) {
+  __shared__ float ms[MAX_KSPLITS], ls[MAX_KSPLITS];
   pdl_release_next();
   pdl_wait_prior();
   const int row = blockIdx.x, t = row / H, h = row % H;
   const float* src = part + (size_t)row * ksplits * (2 + RANK);
-  float M = -INFINITY;
-  for (int s = 0; s < ksplits; ++s) M = fmaxf(M, src[(size_t)s * (2 + RANK)]);
-  float L = 0.f;
-  for (int s = 0; s < ksplits; ++s) {
-    const float m = src[(size_t)s * (2 + RANK)];
-    if (m > -INFINITY) L += src[(size_t)s * (2 + RANK) + 1] * exp2f(m - M);
+  if (threadIdx.x < ksplits) {
+    ms[threadIdx.x] = src[(size_t)threadIdx.x * (2 + RANK)];
+    ls[threadIdx.x] = src[(size_t)threadIdx.x * (2 + RANK) + 1];
   }
+  __syncthreads();
+  float M = -INFINITY;
+  for (int s = 0; s < ksplits; ++s) M = fmaxf(M, ms[s]);
+  float L = 0.f;
+  for (int s = 0; s < ksplits; ++s) L += ms[s] > -INFINITY ? ls[s] * exp2f(ms[s] - M) : 0.f;
   for (int d = threadIdx.x; d < RANK; d += 128) {
     float acc = 0.f;
+#pragma unroll 8
     for (int s = 0; s < ksplits; ++s) {
-      const float m = src[(size_t)s * (2 + RANK)];
-      if (m > -INFINITY) acc += src[(size_t)s * (2 + RANK) + 2 + d] * exp2f(m - M);
+      const float v = src[(size_t)s * (2 + RANK) + 2 + d];     // a split without keys left zeros
+      acc += ms[s] > -INFINITY ? v * exp2f(ms[s] - M) : 0.f;
     }
     out[(size_t)t * ldo + (size_t)h * RANK + d] = __float2bfloat16_rn(acc / L);
   }
@@ -292,14 +315,14 @@ GB_EXPORT int gb_latent_attention_mma(const void* qa, long long ldq, void* out, 
                                       int ntok, int H, int rank, int rot, int max_rows, int window, int ksplits,
                                       cudaStream_t stream) {
   if (ntok <= 0 || n_seqs <= 0) return 0;
-  if (rank != RANK || rot != ROT || H <= 0 || page_size % KEYS || ksplits < 1) return GB_ERR_SIZE;
+  if (rank != RANK || rot != ROT || H <= 0 || page_size % KEYS || ksplits < 1 || ksplits > MAX_KSPLITS) return GB_ERR_SIZE;
   if (((uintptr_t)qa & 15) || (ldq % 8) || ((uintptr_t)out & 3) || (ldo % 2) || ((uintptr_t)cache & 15)) return GB_ERR_SIZE;
   if (ksplits > 1 && part == nullptr) return GB_ERR_ARG;
   int groups = (max_rows + 15) / 16;
   groups = groups < 1 ? 1 : (groups > MAX_GROUPS ? MAX_GROUPS : groups);
   const int tile_rows = groups * 16;
-  const size_t smem = ((size_t)tile_rows * LDS + 2 * (size_t)KEYS * LDS) * sizeof(bf16) +
-                      (NSPLIT > 1 ? (size_t)groups * 16 * SXP * sizeof(float) : 0);
+  const size_t smem = 2 * (size_t)KEYS * LDS * sizeof(bf16) +
+                      (NSPLIT > 1 ? (size_t)groups * NSPLIT * 16 * SXP * sizeof(float) : 0);
   static size_t allowed = 0;
   if (smem > allowed) {
     if (cudaFuncSetAttribute(latent_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)

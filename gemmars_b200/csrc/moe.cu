@@ -6,10 +6,12 @@
 //              y = g * sigmoid(alpha g) * (u + shift);  out = down y
 //   residual[t] += sum over chosen of weight * expert_e(h[t])  +  sigmoid(sg . h[t]) * shared(h[t])
 //
-// Token-major: a block owns one (token, chosen expert) pair and a run of the expert's features,
-// so the kernels need nothing from the host about who chose what and run inside captured steps.
-// A token's experts are added in the order of its chosen list, then the shared expert: the same
-// bits whatever else is in the batch.  All sums are float32.
+// The router's logits are a product like any other (the part computes them in float32); this unit
+// picks the experts from them and runs the experts token-major: a block owns one (token, chosen
+// expert) pair and a run of the expert's features, so the kernels need nothing from the host about
+// who chose what and run inside captured steps.  Every pair's down product leaves a weighted
+// float32 row, and a token's rows are added into the residual in the order of its chosen list,
+// then the shared expert: the same bits whatever else is in the batch.  All sums are float32.
 #include "common.cuh"
 
 template <typename T> struct Vec;
@@ -47,37 +49,58 @@ __device__ __forceinline__ float lane_dot(const T* __restrict__ row, const float
   return acc;
 }
 
+// Two rows against the same xs at once: twice the loads in flight.
+template <typename T>
+__device__ __forceinline__ void lane_dot2(const T* __restrict__ r0, const T* __restrict__ r1, const float* __restrict__ xs,
+                                          int n, int lane, bool vec, float& a0, float& a1) {
+  a0 = a1 = 0.f;
+  if (vec) {
+    constexpr int V = Vec<T>::N;
+    const typename Vec<T>::type* p0 = (const typename Vec<T>::type*)r0;
+    const typename Vec<T>::type* p1 = (const typename Vec<T>::type*)r1;
+#pragma unroll 2
+    for (int i = lane; i < n / V; i += 32) {
+      float f0[V], f1[V];
+      const typename Vec<T>::type v0 = p0[i], v1 = p1[i];
+      unpack(v0, f0);
+      unpack(v1, f1);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float x = xs[i * V + k];
+        a0 = fmaf(f0[k], x, a0);
+        a1 = fmaf(f1[k], x, a1);
+      }
+    }
+  } else {
+    for (int i = lane; i < n; i += 32) {
+      a0 = fmaf(to_f32(r0[i]), xs[i], a0);
+      a1 = fmaf(to_f32(r1[i]), xs[i], a1);
+    }
+  }
+}
+
 template <typename T> __device__ __forceinline__ bool rows_vectorize(const T* base, int n) {
   return n % Vec<T>::N == 0 && ((uintptr_t)base & 15) == 0;
 }
 
-// ---- router: one block of 128 threads per token
-template <typename T>
-__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h, long long ldh,
-                                                        const float* __restrict__ router, const float* __restrict__ bias,
-                                                        const float* __restrict__ sg_w, int* __restrict__ idx,
-                                                        float* __restrict__ wts, float* __restrict__ sg, int width, int E,
-                                                        int top) {
+// ---- router: the logits come from a product (float32 [ntok, ldz]); a warp per token adds the
+// bias, picks the `top` largest (the lower index wins a tie) and takes the softmax over those
+// alone.  Column E of z, when there is one, is the shared expert's gate logit.
+__global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__ zin, long long ldz,
+                                                       const float* __restrict__ bias, int* __restrict__ idx,
+                                                       float* __restrict__ wts, float* __restrict__ sg, int ntok, int E,
+                                                       int top, int has_gate) {
   extern __shared__ float smem[];
   pdl_release_next();
   pdl_wait_prior();
-  float* xs = smem;              // [width]
-  float* z = smem + width;       // [E]
-  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int i = tid; i < width; i += 128) xs[i] = to_f32(h[(size_t)t * ldh + i]);
-  __syncthreads();
-  const bool vec = rows_vectorize(router, width);
-  for (int e = warp; e < E + (sg_w ? 1 : 0); e += 4) {
-    const float* row = e < E ? router + (size_t)e * width : sg_w;
-    const float d = warp_sum(lane_dot(row, xs, width, lane, vec && rows_vectorize(row, width)));
-    if (lane == 0) {
-      if (e < E) z[e] = d + (bias ? bias[e] : 0.f);
-      else sg[t] = 1.0f / (1.0f + expf(-d));
-    }
-  }
-  __syncthreads();
-  if (warp != 0) return;
-  float mine = 0.f, first = 0.f, sum = 0.f;   // lane k keeps the k-th chosen logit
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= ntok) return;
+  float* z = smem + (size_t)warp * E;
+  for (int e = lane; e < E; e += 32) z[e] = zin[(size_t)t * ldz + e] + (bias ? bias[e] : 0.f);
+  if (has_gate && lane == 0) sg[t] = 1.0f / (1.0f + expf(-zin[(size_t)t * ldz + E]));
+  __syncwarp();
+  float mine = 0.f, first = 0.f;   // lane k keeps the k-th chosen logit
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int at = 0x7fffffff;
@@ -100,7 +123,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h,
     __syncwarp();
   }
   const float e = lane < top ? expf(mine - first) : 0.f;
-  sum = warp_sum(e);
+  const float sum = warp_sum(e);
   if (lane < top) wts[(size_t)t * top + lane] = e / sum;
 }
 
@@ -128,8 +151,10 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T* __restrict__ 
   __syncthreads();
   const bool vec = rows_vectorize(W, width);
   for (int f = f0 + warp; f < min(nf, f0 + FEATS); f += 8) {
-    float g = warp_sum(lane_dot(W + (size_t)f * width, xs, width, lane, vec));
-    float u = warp_sum(lane_dot(W + (size_t)(nf + f) * width, xs, width, lane, vec));
+    float g, u;
+    lane_dot2(W + (size_t)f * width, W + (size_t)(nf + f) * width, xs, width, lane, vec, g, u);
+    g = warp_sum(g);
+    u = warp_sum(u);
     if (lane == 0) {
       g = fminf(g, lim);
       u = fminf(fmaxf(u, -lim), lim);
@@ -139,48 +164,58 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T* __restrict__ 
   }
 }
 
-// ---- down of all of a token's slots, weighted and added into the residual
+// ---- down of one (token, slot), weighted, into a float32 row of its own; the rows of a token are
+// added into the residual in slot order by moe_sum_kernel
 template <typename T>
 __global__ void __launch_bounds__(256) moe_down_kernel(const T* __restrict__ y, const int* __restrict__ idx,
                                                        const float* __restrict__ wts, const float* __restrict__ sg,
                                                        const T* __restrict__ w_d, const T* __restrict__ ws_d,
-                                                       float* __restrict__ residual, long long ldr, int width, int ff,
-                                                       int ffs, int ffmax, int top, int slots) {
-  extern __shared__ float ys[];   // [slots, ffmax]
+                                                       float* __restrict__ rows, int width, int ff, int ffs, int ffmax,
+                                                       int top, int slots) {
+  extern __shared__ float ys[];   // [ffmax]
   pdl_release_next();
   pdl_wait_prior();
-  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int i = tid; i < slots * ffmax; i += 256) ys[i] = to_f32(y[(size_t)t * slots * ffmax + i]);
+  const int t = blockIdx.x / slots, s = blockIdx.x % slots;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool routed = s < top;
+  const int nf = routed ? ff : ffs;
+  for (int i = tid; i < nf; i += 256) ys[i] = to_f32(y[((size_t)t * slots + s) * ffmax + i]);
   __syncthreads();
+  const T* W = routed ? w_d + (size_t)idx[(size_t)t * top + s] * width * ff : ws_d;
+  const float wt = routed ? wts[(size_t)t * top + s] : sg[t];
+  const bool vec = rows_vectorize(W, nf);
   const int n0 = blockIdx.y * FEATS;
-  for (int n = n0 + warp; n < min(width, n0 + FEATS); n += 8) {
-    float total = 0.f;
-    for (int s = 0; s < slots; ++s) {
-      const bool routed = s < top;
-      const int nf = routed ? ff : ffs;
-      const T* row = routed ? w_d + ((size_t)idx[(size_t)t * top + s] * width + n) * ff : ws_d + (size_t)n * ffs;
-      const float d = warp_sum(lane_dot(row, ys + (size_t)s * ffmax, nf, lane, rows_vectorize(row, nf) && ffmax % 4 == 0));
-      total += d * (routed ? wts[(size_t)t * top + s] : sg[t]);
+  for (int n = n0 + warp * 2; n < min(width, n0 + FEATS); n += 16) {
+    float a, b;
+    const bool two = n + 1 < width;
+    lane_dot2(W + (size_t)n * nf, W + (size_t)(two ? n + 1 : n) * nf, ys, nf, lane, vec, a, b);
+    a = warp_sum(a);
+    b = warp_sum(b);
+    if (lane == 0) {
+      rows[((size_t)t * slots + s) * width + n] = a * wt;
+      if (two) rows[((size_t)t * slots + s) * width + n + 1] = b * wt;
     }
-    if (lane == 0) residual[(size_t)t * ldr + n] += total;
   }
 }
 
-GB_EXPORT int gb_moe_route(const void* h, long long ldh, int dtype, const float* router, const float* bias,
-                           const float* sg_w, int* idx, float* wts, float* sg, int ntok, int width, int E, int top,
-                           cudaStream_t stream) {
+__global__ void __launch_bounds__(256) moe_sum_kernel(const float* __restrict__ rows, float* __restrict__ residual,
+                                                      long long ldr, int width, int slots) {
+  pdl_release_next();
+  pdl_wait_prior();
+  const int t = blockIdx.x;
+  for (int n = blockIdx.y * 256 + threadIdx.x; n < width; n += gridDim.y * 256) {
+    float total = 0.f;
+    for (int s = 0; s < slots; ++s) total += rows[((size_t)t * slots + s) * width + n];
+    residual[(size_t)t * ldr + n] += total;
+  }
+}
+
+GB_EXPORT int gb_moe_topk(const float* z, long long ldz, const float* bias, int* idx, float* wts, float* sg, int ntok,
+                          int E, int top, int has_gate, cudaStream_t stream) {
   if (ntok <= 0) return 0;
-  if (E <= 0 || top <= 0 || top > 32 || top > E || width <= 0) return GB_ERR_SIZE;
-  const size_t smem = (size_t)(width + E) * sizeof(float);
-  if (smem > 48 * 1024) return GB_ERR_SIZE;
-  if (dtype == GB_F32)
-    gb_launch(moe_route_kernel<float>, dim3(ntok), dim3(128), smem, stream, (const float*)h, ldh, router, bias, sg_w, idx,
-              wts, sg, width, E, top);
-  else if (dtype == GB_BF16)
-    gb_launch(moe_route_kernel<bf16>, dim3(ntok), dim3(128), smem, stream, (const bf16*)h, ldh, router, bias, sg_w, idx,
-              wts, sg, width, E, top);
-  else
-    return GB_ERR_DTYPE;
+  if (E <= 0 || top <= 0 || top > 32 || top > E || E > 2048) return GB_ERR_SIZE;
+  gb_launch(moe_topk_kernel, dim3((ntok + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), stream, z, ldz, bias, idx, wts, sg,
+            ntok, E, top, has_gate);
   return gb_launch_status();
 }
 
@@ -206,26 +241,26 @@ GB_EXPORT int gb_moe_gate_up(const void* h, long long ldh, int dtype, const int*
   return gb_launch_status();
 }
 
-// w_d: [E, width, ff]; ws_d: [width, ffs] or null; residual: float32 [ntok, width] rows ldr apart.
+// w_d: [E, width, ff]; ws_d: [width, ffs] or null; rows: float32 scratch [ntok, slots, width];
+// residual: float32 [ntok, width] rows ldr apart.
 GB_EXPORT int gb_moe_down(const void* y, int dtype, const int* idx, const float* wts, const float* sg, const void* w_d,
-                          const void* ws_d, float* residual, long long ldr, int ntok, int width, int ff, int ffs, int top,
-                          cudaStream_t stream) {
+                          const void* ws_d, float* rows, float* residual, long long ldr, int ntok, int width, int ff, int ffs,
+                          int top, cudaStream_t stream) {
   if (ntok <= 0) return 0;
   const int slots = top + (ws_d ? 1 : 0), ffmax = ff > ffs ? ff : ffs;
   if (width <= 0 || ffmax <= 0 || slots <= 0) return GB_ERR_SIZE;
-  const size_t smem = (size_t)slots * ffmax * sizeof(float);
-  if (smem > 200 * 1024) return GB_ERR_SIZE;
-  dim3 grid(ntok, (width + FEATS - 1) / FEATS);
-  if (dtype == GB_F32) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const size_t smem = (size_t)ffmax * sizeof(float);
+  if (smem > 48 * 1024) return GB_ERR_SIZE;
+  dim3 grid(ntok * slots, (width + FEATS - 1) / FEATS);
+  if (dtype == GB_F32)
     gb_launch(moe_down_kernel<float>, grid, dim3(256), smem, stream, (const float*)y, idx, wts, sg, (const float*)w_d,
-              (const float*)ws_d, residual, ldr, width, ff, ffs, ffmax, top, slots);
-  } else if (dtype == GB_BF16) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+              (const float*)ws_d, rows, width, ff, ffs, ffmax, top, slots);
+  else if (dtype == GB_BF16)
     gb_launch(moe_down_kernel<bf16>, grid, dim3(256), smem, stream, (const bf16*)y, idx, wts, sg, (const bf16*)w_d,
-              (const bf16*)ws_d, residual, ldr, width, ff, ffs, ffmax, top, slots);
-  } else {
+              (const bf16*)ws_d, rows, width, ff, ffs, ffmax, top, slots);
+  else
     return GB_ERR_DTYPE;
-  }
+  gb_launch(moe_sum_kernel, dim3(ntok, (width + 1023) / 1024), dim3(256), 0, stream, (const float*)rows, residual, ldr, width,
+            slots);
   return gb_launch_status();
 }

@@ -862,9 +862,10 @@ def heads_gemm(x, w, y, heads, scale=None):
            _nbytes(w) + t * heads * (n + k) * x.element_size())
 
 
-# below this many tokens the per-head products are a matrix-vector job: the FFMA kernel's 64-row
-# tiles read the weights once either way, and a 128-row tensor-core tile would be nearly empty
-HEADS_GEMM_TC_MIN_TOKENS = 17
+# the tensor-core kernel from the first token on: inside a replayed decode step of 8 tokens the FFMA
+# kernel took 20 and 58 us for the two products of a layer (16 heads, 128 -> 512 and 512 -> 128), one
+# scalar load per element and 64 x 16 blocks in turn; a nearly empty 128-row tile costs nothing here
+HEADS_GEMM_TC_MIN_TOKENS = 1
 
 
 def grouped_gemm(a, lda, a_gstride, a_rows, a_div, w, w_gstride, c, ldc, c_gstride, scale, scale_rows, s_rstride, s_gstride,
@@ -958,9 +959,10 @@ def latent_attention_mma(qa, out, heads, rank, rd, cache, page_table, page_size,
 
 
 def latent_decode_splits(n_seqs: int, heads: int) -> int:
-    """CTAs along the keys for each sequence of a decode step: about one CTA per SM in all."""
-    tiles = n_seqs * -(-heads // 64)
-    return max(1, min(32, sm_count() // max(tiles, 1)))
+    """CTAs along the keys for each sequence of a decode step: about two CTAs per SM in all (a CTA is
+    one group of 16 rows, few warps; two to an SM hide each other's waits)."""
+    tiles = n_seqs * -(-heads // 32)
+    return max(1, min(64, (2 * sm_count()) // max(tiles, 1)))
 
 
 def latent_attention(ctx, qa, out, heads, rank, rd, cache, page_table, page_size, window=None):
@@ -990,24 +992,21 @@ def latent_attention_units(compute: str, rank: int, rd: int):
 
 # --------------------------------------------------------------------------- routed feed-forward
 
-def moe_route(h, router, bias, shared_gate, top):
-    """(idx int32 [T, top], weights float32 [T, top], shared float32 [T] or None): each token's
-    ``top`` largest router logits (router [E, width] and bias [E] in float32; the lower index wins
-    a tie), the softmax over those alone, and sigmoid(shared_gate . h) when a gate row is given."""
-    _cuda(h, router, bias, shared_gate)
-    t, width = h.shape
-    e = router.shape[0]
-    assert router.dtype == torch.float32 and router.shape == (e, width) and router.is_contiguous() and h.stride(1) == 1
-    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == e)
-    assert shared_gate is None or (shared_gate.dtype == torch.float32 and shared_gate.numel() == width)
-    idx = torch.empty((t, top), dtype=torch.int32, device=h.device)
-    wts = torch.empty((t, top), dtype=torch.float32, device=h.device)
-    sg = torch.empty((t,), dtype=torch.float32, device=h.device) if shared_gate is not None else None
-    f = _fn("moe", "gb_moe_route", [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                    c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(h.data_ptr(), h.stride(0), dtype_code(h.dtype), router.data_ptr(), _ptr(bias), _ptr(shared_gate),
-             idx.data_ptr(), wts.data_ptr(), _ptr(sg), t, width, e, top, _stream()), "moe_route", "matmul",
-           _nbytes(h, router))
+def moe_topk(z, bias, experts, top, has_gate=False):
+    """(idx int32 [T, top], weights float32 [T, top], shared float32 [T] or None) from the router's
+    logits z (float32 [T, experts (+ 1)]): each token's ``top`` largest z + bias (the lower index wins
+    a tie), the softmax over those alone, and with ``has_gate`` the sigmoid of column ``experts``."""
+    _cuda(z, bias)
+    t = z.shape[0]
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and z.shape[1] >= experts + (1 if has_gate else 0)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == experts)
+    idx = torch.empty((t, top), dtype=torch.int32, device=z.device)
+    wts = torch.empty((t, top), dtype=torch.float32, device=z.device)
+    sg = torch.empty((t,), dtype=torch.float32, device=z.device) if has_gate else None
+    f = _fn("moe", "gb_moe_topk", [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                   c_void_p])
+    _check(f(z.data_ptr(), z.stride(0), _ptr(bias), idx.data_ptr(), wts.data_ptr(), _ptr(sg), t, experts, top,
+             1 if has_gate else 0, _stream()), "moe_topk", "elementwise", _nbytes(z))
     return idx, wts, sg
 
 
@@ -1034,11 +1033,13 @@ def moe_experts(h, idx, wts, sg, w_gate_up, w_down, shared_gate_up, shared_down,
     _check(f(h.data_ptr(), h.stride(0), dtype_code(h.dtype), idx.data_ptr(), w_gate_up.data_ptr(), _ptr(shared_gate_up),
              y.data_ptr(), t, width, ff, ffs, top, limit, shared_limit, alpha, shift, _stream()), "moe_gate_up", "matmul",
            _nbytes(h, y) + t * slots * 2 * ff * width * h.element_size())
-    f = _fn("moe", "gb_moe_down", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
-                                   c_int, c_int, c_int, c_int, c_int, c_void_p])
+    rows = torch.empty((t, slots, width), dtype=torch.float32, device=h.device)
+    f = _fn("moe", "gb_moe_down", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(f(y.data_ptr(), dtype_code(h.dtype), idx.data_ptr(), wts.data_ptr(), _ptr(sg), w_down.data_ptr(),
-             _ptr(shared_down), residual.data_ptr(), residual.stride(0), t, width, ff, ffs, top, _stream()), "moe_down",
-           "matmul", _nbytes(y) + 2 * t * width * 4 + t * slots * ff * width * h.element_size())
+             _ptr(shared_down), rows.data_ptr(), residual.data_ptr(), residual.stride(0), t, width, ff, ffs, top, _stream()),
+           "moe_down", "matmul", _nbytes(y) + 2 * _nbytes(rows) + 2 * t * width * 4 + t * slots * ff * width * h.element_size())
+    count_launches(1)   # the kernel that adds a token's rows
 
 
 MOE_GROUPED_MIN_TOKENS = 16

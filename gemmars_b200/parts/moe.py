@@ -1,6 +1,6 @@
 """Routed feed-forward (mixture of experts) with an optional shared expert.
 
-    z        = router h + bias                      float32
+    z        = router h + bias                      float32 (a product of the framework's, written in float32)
     chosen   = the ``top`` largest z;  weights = softmax over the chosen z alone
     expert   : g = min(gate h, limit), u = clamp(up h, -limit, limit)
                y = g * sigmoid(alpha g) * (u + shift);  out = down y        (no biases)
@@ -18,6 +18,7 @@ import torch
 
 from .. import kernels
 from .base import Part, TensorWant, register_part
+from .linear import Linear
 
 
 class RoutedExperts(Part):
@@ -41,11 +42,11 @@ class RoutedExperts(Part):
         if not 1 <= self.top <= min(self.experts, 32):
             raise ValueError(f"moe: top {self.top} of {self.experts} experts is not supported (1 to 32, at most all)")
         self.router = self.bias = self.gate_up = self.down = None
-        self.shared_gate_up = self.shared_down = self.shared_gate = None
+        self.shared_gate_up = self.shared_down = None
 
     def wants(self):
         h, f = self.hidden_size, self.ff
-        w = {"router": TensorWant((self.experts, h), "vector")}
+        w = {"router": TensorWant((self.experts, h))}
         if self.router_bias:
             w["router_bias"] = TensorWant((self.experts,), "vector")
         for e in range(self.experts):
@@ -57,36 +58,38 @@ class RoutedExperts(Part):
             w.update({"shared.gate": TensorWant((fs, h)), "shared.up": TensorWant((fs, h)),
                       "shared.down": TensorWant((h, fs))})
             if self.shared_gated:
-                w["shared.sg"] = TensorWant((1, h), "vector")
+                w["shared.sg"] = TensorWant((1, h))
         return w
 
     def load(self, t):
-        self.router = t["router"].contiguous()
+        gate_row = [t["shared.sg"].reshape(1, -1)] if self.shared_ff and self.shared_gated else []
+        # the router's logits and the shared expert's gate logit are one product, written in float32
+        self.router = Linear(torch.cat([t["router"]] + gate_row, dim=0))
         self.bias = t["router_bias"].contiguous() if self.router_bias else None
         self.gate_up = torch.stack([torch.cat([t[f"e{e}.gate"], t[f"e{e}.up"]], dim=0) for e in range(self.experts)])
         self.down = torch.stack([t[f"e{e}.down"] for e in range(self.experts)])
         if self.shared_ff:
             self.shared_gate_up = torch.cat([t["shared.gate"], t["shared.up"]], dim=0).contiguous()
             self.shared_down = t["shared.down"].contiguous()
-            if self.shared_gated:
-                self.shared_gate = t["shared.sg"].reshape(-1).contiguous()
-            else:   # sigmoid(30) is 1 in float32: an ungated shared expert is one whose gate is always open
-                self.shared_gate = None
 
     def kernel_units(self):
         if self.compute == "float32":
-            return [("moe", ())]
+            return [("moe", ())] + kernels.gemm_units(self.compute)
         return [("moe", ()), ("grouped_gemm", ())] + kernels.gemm_units(self.compute)
+
+    def _route(self, h):
+        z = self.router(h, out_dtype=torch.float32)
+        return kernels.moe_topk(z, self.bias, self.experts, self.top, has_gate=bool(self.shared_ff and self.shared_gated))
 
     def weight_bytes(self):
         """What a decode step of one token reads: the router, ``top`` experts, the shared expert."""
         per = self.gate_up.element_size()
         one = 3 * self.ff * self.hidden_size * per
         shared = 3 * self.shared_ff * self.hidden_size * per
-        return 4 * self.router.numel() + self.top * one + shared
+        return self.router.bytes() + self.top * one + shared
 
     def forward(self, ctx, h, residual):
-        idx, wts, sg = kernels.moe_route(h, self.router, self.bias, self.shared_gate, self.top)
+        idx, wts, sg = self._route(h)
         if self.shared_ff and sg is None:
             sg = torch.ones((h.shape[0],), dtype=torch.float32, device=h.device)
         run = kernels.moe_experts_grouped if kernels.moe_grouped_usable(h, self.gate_up, self.down) else kernels.moe_experts

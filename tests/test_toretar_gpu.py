@@ -215,22 +215,22 @@ def test_attention_over_latents_finds_planted_keys(dtype, heads, rank, rd, decod
                 assert np.abs(got[r].reshape(heads, rank) - rows_of_seq[s][key][:rank]).max() < 0.05
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("t,width,experts,top", [(9, 72, 5, 2), (70, 128, 8, 8), (3, 40, 3, 1), (33, 96, 40, 6)])
-def test_router(dtype, t, width, experts, top):
+@pytest.mark.parametrize("t,experts,top", [(9, 5, 2), (70, 8, 8), (3, 3, 1), (33, 40, 6), (5, 300, 32)])
+def test_expert_choice_from_the_logits(t, experts, top):
     from gemmars_b200 import kernels
     rng = np.random.default_rng(5)
-    h, hn = _rand(rng, (t, width), _dt(dtype))
-    r, rn = _rand(rng, (experts, width), torch.float32)
+    z, zn = _rand(rng, (t, experts + 1), torch.float32)
     b, bn = _rand(rng, (experts,), torch.float32)
-    sg, sgn = _rand(rng, (width,), torch.float32)
-    idx, wts, gate = kernels.moe_route(h, r, b, sg, top)
-    want_idx, want_w = plain.route(hn, rn, bn, top)
+    idx, wts, gate = kernels.moe_topk(z, b, experts, top, has_gate=True)
+    logits = zn[:, :experts] + bn
+    want_idx = np.argsort(-logits, axis=-1, kind="stable")[:, :top]
     assert np.array_equal(idx.cpu().numpy(), want_idx)
-    assert np.abs(wts.double().cpu().numpy() - want_w).max() < 1e-5
-    assert np.abs(gate.double().cpu().numpy() - plain.sigmoid(hn @ sgn)).max() < 1e-5
-    idx2, wts2, none = kernels.moe_route(h, r, None, None, top)
-    assert none is None and np.array_equal(idx2.cpu().numpy(), plain.route(hn, rn, 0 * bn, top)[0])
+    assert np.abs(wts.double().cpu().numpy() - plain.softmax(np.take_along_axis(logits, want_idx, -1))).max() < 1e-6
+    assert np.abs(gate.double().cpu().numpy() - plain.sigmoid(zn[:, experts])).max() < 1e-6
+    z[:, 1] = z[:, 0]                               # a tie goes to the lower index
+    idx2, _, none = kernels.moe_topk(z, None, experts, top)
+    order = np.argsort(-z.cpu().numpy()[:, :experts], axis=-1, kind="stable")[:, :top]
+    assert none is None and np.array_equal(idx2.cpu().numpy(), order)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -244,7 +244,7 @@ def test_routed_feed_forward(dtype, t, width, experts, top, ff, ffs):
     dt = _dt(dtype)
     names, w, wn = {}, {}, {}
     def add(short, shape, scale, f32=False):
-        w[short], wn["p." + short.replace("router_bias", "router.b")] = _rand(rng, shape, torch.float32 if f32 else dt, scale)
+        w[short], wn["p." + short.replace("router_bias", "router.b")] = _rand(rng, shape, dt, scale)
         names[short] = short
     add("router", (experts, width), 0.3)
     add("router_bias", (experts,), 0.3)
@@ -261,7 +261,7 @@ def test_routed_feed_forward(dtype, t, width, experts, top, ff, ffs):
            "shared": {"ff": ffs, "limit": 1.7} if ffs else None}
     part = build_part("ffn", PartSpec("moe", {"hidden_size": width, "experts": experts, "top": top, "ff": ff, "limit": 0.8,
                                               "shared": {"ff": ffs, "limit": 1.7} if ffs else None}, names), dtype)
-    part.load({k: (v.float() if part.wants()[k].role == "vector" else v) for k, v in w.items()})
+    part.load({k: (v.float() if part.wants()[k].role == "vector" else v.to(dt)) for k, v in w.items()})
     h, hn = _rand(rng, (t, width), dt)
     res, resn = _rand(rng, (t, width), torch.float32)
     ctx = type("Ctx", (), dict(host=None))()
