@@ -118,7 +118,13 @@ def decode_bytes(model, runner, lengths):
         per_token = g.n_layers * g.need.num_kv_heads * (g.need.head_dim + _value_dim(g)) * g.k.element_size()
         for n in lengths:
             kv += per_token * (min(n, g.need.window) if g.need.window else n)
-    return model.weight_bytes() + kv
+    # a part whose reads grow with the batch (routed experts: every expert some token chose) says so itself
+    extra = 0
+    for block in model.blocks:
+        for part in block.parts().values():
+            if hasattr(part, "decode_bytes"):
+                extra += part.decode_bytes(len(lengths)) - part.weight_bytes()
+    return model.weight_bytes() + extra + kv
 
 
 def prefill_flops(cfg, t):

@@ -88,6 +88,15 @@ class RoutedExperts(Part):
         shared = 3 * self.shared_ff * self.hidden_size * per
         return self.router.bytes() + self.top * one + shared
 
+    def decode_bytes(self, batch: int) -> int:
+        """What a decode step of ``batch`` tokens has to read at least: the router, the shared expert,
+        and every expert that some token chose, once; with choices spread evenly that is
+        experts * (1 - (1 - top / experts) ** batch) experts on average."""
+        per = self.gate_up.element_size()
+        one = 3 * self.ff * self.hidden_size * per
+        distinct = self.experts * (1.0 - (1.0 - self.top / self.experts) ** max(batch, 1))
+        return int(self.router.bytes() + distinct * one + 3 * self.shared_ff * self.hidden_size * per)
+
     def forward(self, ctx, h, residual):
         idx, wts, sg = self._route(h)
         if self.shared_ff and sg is None:
