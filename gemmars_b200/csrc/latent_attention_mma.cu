@@ -34,16 +34,13 @@ constexpr int RANK = GB_LATENT_RANK, ROT = GB_LATENT_ROT, KD = RANK + ROT;
 static_assert(RANK % 16 == 0 && ROT % 16 == 0 && RANK >= 16, "latent and rotated widths must be multiples of 16");
 constexpr int NSPLIT = RANK <= 128 ? 1 : (RANK <= 256 ? 2 : 4);
 static_assert(RANK % (16 * NSPLIT) == 0, "the latent must divide into 16-column blocks per warp");
-constexpr int KEYS = 64;
 constexpr int LDS = KD + ((KD / 8) % 2 == 0 ? 8 : 0);   // row pitch in shared memory: an odd number of 16-byte units
-constexpr int NB = KEYS / 8;                             // blocks of 8 keys a tile
 constexpr int KSTEPS = KD / 16;                          // 16-column steps of a score
 constexpr int KSW = (KSTEPS + NSPLIT - 1) / NSPLIT;      // steps a warp owns
 constexpr int DW = RANK / NSPLIT;                        // output columns a warp owns
-constexpr int SXP = KEYS + 4;                            // pitch of the exchanged scores
-constexpr int MAX_GROUPS = NSPLIT == 4 ? 2 : 4;          // groups of 16 rows a CTA at most (<= 2 * KEYS rows: the queries' staging)
+constexpr int MAX_GROUPS = NSPLIT == 4 ? 2 : 4;          // groups of 16 rows a CTA at most
+constexpr int PART = RANK + 4;                           // floats of a split's part: o, then m and l (rows stay 16-byte aligned)
 constexpr float LOG2E = 1.4426950408889634f;
-static_assert(NB % 2 == 0 && MAX_GROUPS * 16 <= 2 * KEYS, "key blocks come in pairs; the queries are staged in the key buffers");
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -62,13 +59,18 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t* r, const void* p) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
 
-// grid (row tiles upper bound, ksplits); block groups * NSPLIT * 32.
+// grid (row tiles upper bound, ksplits); block groups * NSPLIT * 32.  KEYS: keys a tile (64 for
+// prompts; 32 for decoding, where two CTAs then share an SM and hide each other's waits).
+template <int KEYS>
 __global__ void __launch_bounds__(MAX_GROUPS * NSPLIT * 32)
 latent_attention_mma_kernel(const bf16* __restrict__ qa, long long ldq, bf16* __restrict__ out, long long ldo,
                             float* __restrict__ part, const bf16* __restrict__ cache, const int* __restrict__ page_table,
                             int table_width, int page_size, const int* __restrict__ cu_seqlens,
                             const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int n_seqs, int H,
                             int window, int ksplits) {
+  constexpr int NB = KEYS / 8;                         // blocks of 8 keys a tile
+  constexpr int SXP = KEYS + 4;                        // pitch of the exchanged scores
+  static_assert(NB % 2 == 0, "key blocks come in pairs");
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_release_next();
   pdl_wait_prior();
@@ -256,19 +258,19 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, long long ldq, bf16* __
     }
     return;
   }
-  // parts: [row of the step][split][2 + RANK]: m (log2 units), l, unnormalised o
+  // parts: [row of the step][split][PART]: unnormalised o, then m (log2 units) and l
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int row = half ? r1 : r0;
     if (!(half ? v1 : v0)) continue;
-    float* dst = part + (((size_t)(tok_base + row / H) * H + row % H) * ksplits + blockIdx.y) * (2 + RANK);
-    if (w == 0 && c == 0) { dst[0] = half ? m1 : m0; dst[1] = half ? l1 : l0; }
+    float* dst = part + (((size_t)(tok_base + row / H) * H + row % H) * ksplits + blockIdx.y) * PART;
+    if (w == 0 && c == 0) { dst[RANK] = half ? m1 : m0; dst[RANK + 1] = half ? l1 : l0; }
 #pragma unroll
-    for (int d = 0; d < DW / 8; ++d) *(float2*)(dst + 2 + w * DW + d * 8 + 2 * c) = make_float2(o[d][2 * half], o[d][2 * half + 1]);
+    for (int d = 0; d < DW / 8; ++d) *(float2*)(dst + w * DW + d * 8 + 2 * c) = make_float2(o[d][2 * half], o[d][2 * half + 1]);
   }
 }
 
-// one block per (token, head): adds the splits' parts in split order
+// one block per (token, head): adds the splits' parts in split order, four columns a thread
 constexpr int MAX_KSPLITS = 64;
 
 __global__ void __launch_bounds__(128) latent_attention_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out,
@@ -277,31 +279,55 @@ __global__ void __launch_bounds__(128) latent_attention_merge_kernel(const float
   pdl_release_next();
   pdl_wait_prior();
   const int row = blockIdx.x, t = row / H, h = row % H;
-  const float* src = part + (size_t)row * ksplits * (2 + RANK);
+  const float* src = part + (size_t)row * ksplits * PART;
   if (threadIdx.x < ksplits) {
-    ms[threadIdx.x] = src[(size_t)threadIdx.x * (2 + RANK)];
-    ls[threadIdx.x] = src[(size_t)threadIdx.x * (2 + RANK) + 1];
+    ms[threadIdx.x] = src[(size_t)threadIdx.x * PART + RANK];
+    ls[threadIdx.x] = src[(size_t)threadIdx.x * PART + RANK + 1];
   }
   __syncthreads();
   float M = -INFINITY;
   for (int s = 0; s < ksplits; ++s) M = fmaxf(M, ms[s]);
   float L = 0.f;
   for (int s = 0; s < ksplits; ++s) L += ms[s] > -INFINITY ? ls[s] * exp2f(ms[s] - M) : 0.f;
-  for (int d = threadIdx.x; d < RANK; d += 128) {
-    float acc = 0.f;
+  const float inv = 1.0f / L;
+  for (int d = 4 * threadIdx.x; d < RANK; d += 4 * 128) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
     for (int s = 0; s < ksplits; ++s) {
-      const float v = src[(size_t)s * (2 + RANK) + 2 + d];     // a split without keys left zeros
-      acc += ms[s] > -INFINITY ? v * exp2f(ms[s] - M) : 0.f;
+      const float4 v = *(const float4*)(src + (size_t)s * PART + d);     // a split without keys left zeros
+      const float wgt = ms[s] > -INFINITY ? exp2f(ms[s] - M) : 0.f;
+      acc.x += v.x * wgt; acc.y += v.y * wgt; acc.z += v.z * wgt; acc.w += v.w * wgt;
     }
-    out[(size_t)t * ldo + (size_t)h * RANK + d] = __float2bfloat16_rn(acc / L);
+    bf16* dst = out + (size_t)t * ldo + (size_t)h * RANK + d;
+    *(uint32_t*)dst = pack_bf16(acc.x * inv, acc.y * inv);
+    *(uint32_t*)(dst + 2) = pack_bf16(acc.z * inv, acc.w * inv);
   }
+}
+
+template <int KEYS>
+int launch_latent(const bf16* qa, long long ldq, bf16* out, long long ldo, float* part, const bf16* cache, const int* page_table,
+                  int table_width, int page_size, const int* cu_seqlens, const int* seq_start, const int* seq_slot, int n_seqs,
+                  int ntok, int H, int groups, int window, int ksplits, cudaStream_t stream) {
+  const int tile_rows = groups * 16;
+  if (tile_rows > 2 * KEYS) return GB_ERR_SIZE;       // the queries are staged in the key buffers
+  const size_t smem = 2 * (size_t)KEYS * LDS * sizeof(bf16) +
+                      (NSPLIT > 1 ? (size_t)groups * NSPLIT * 16 * (KEYS + 4) * sizeof(float) : 0);
+  static size_t allowed = 0;
+  if (smem > allowed) {
+    if (cudaFuncSetAttribute(latent_attention_mma_kernel<KEYS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return GB_ERR_SIZE;
+    allowed = smem;
+  }
+  dim3 grid(((long long)ntok * H + tile_rows - 1) / tile_rows + n_seqs, ksplits);
+  gb_launch(latent_attention_mma_kernel<KEYS>, grid, dim3(groups * NSPLIT * 32), smem, stream, qa, ldq, out, ldo, part, cache,
+            page_table, table_width, page_size, cu_seqlens, seq_start, seq_slot, n_seqs, H, window, ksplits);
+  return 0;
 }
 
 }  // namespace
 
 GB_EXPORT long long gb_latent_attention_mma_scratch(int ntok, int H, int ksplits) {
-  return ksplits > 1 ? (long long)ntok * H * ksplits * (2 + RANK) : 0;
+  return ksplits > 1 ? (long long)ntok * H * ksplits * PART : 0;
 }
 
 // qa: [ntok, H * (RANK + ROT)] bfloat16 rows ldq apart, packed by sequence (cu_seqlens [n_seqs + 1]);
@@ -315,24 +341,19 @@ GB_EXPORT int gb_latent_attention_mma(const void* qa, long long ldq, void* out, 
                                       int ntok, int H, int rank, int rot, int max_rows, int window, int ksplits,
                                       cudaStream_t stream) {
   if (ntok <= 0 || n_seqs <= 0) return 0;
-  if (rank != RANK || rot != ROT || H <= 0 || page_size % KEYS || ksplits < 1 || ksplits > MAX_KSPLITS) return GB_ERR_SIZE;
+  if (rank != RANK || rot != ROT || H <= 0 || page_size % 64 || ksplits < 1 || ksplits > MAX_KSPLITS) return GB_ERR_SIZE;
   if (((uintptr_t)qa & 15) || (ldq % 8) || ((uintptr_t)out & 3) || (ldo % 2) || ((uintptr_t)cache & 15)) return GB_ERR_SIZE;
-  if (ksplits > 1 && part == nullptr) return GB_ERR_ARG;
+  if (ksplits > 1 && (part == nullptr || ((uintptr_t)part & 15))) return GB_ERR_ARG;
   int groups = (max_rows + 15) / 16;
   groups = groups < 1 ? 1 : (groups > MAX_GROUPS ? MAX_GROUPS : groups);
-  const int tile_rows = groups * 16;
-  const size_t smem = 2 * (size_t)KEYS * LDS * sizeof(bf16) +
-                      (NSPLIT > 1 ? (size_t)groups * NSPLIT * 16 * SXP * sizeof(float) : 0);
-  static size_t allowed = 0;
-  if (smem > allowed) {
-    if (cudaFuncSetAttribute(latent_attention_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return GB_ERR_SIZE;
-    allowed = smem;
-  }
-  dim3 grid(((long long)ntok * H + tile_rows - 1) / tile_rows + n_seqs, ksplits);
-  gb_launch(latent_attention_mma_kernel, grid, dim3(groups * NSPLIT * 32), smem, stream, (const bf16*)qa, ldq, (bf16*)out, ldo,
-            part, (const bf16*)cache, page_table, table_width, page_size, cu_seqlens, seq_start, seq_slot, n_seqs, H, window,
-            ksplits);
+  int rc;
+  if (ksplits > 1)
+    rc = launch_latent<32>((const bf16*)qa, ldq, (bf16*)out, ldo, part, (const bf16*)cache, page_table, table_width, page_size,
+                           cu_seqlens, seq_start, seq_slot, n_seqs, ntok, H, groups, window, ksplits, stream);
+  else
+    rc = launch_latent<64>((const bf16*)qa, ldq, (bf16*)out, ldo, part, (const bf16*)cache, page_table, table_width, page_size,
+                           cu_seqlens, seq_start, seq_slot, n_seqs, ntok, H, groups, window, ksplits, stream);
+  if (rc) return rc;
   if (ksplits > 1)
     gb_launch(latent_attention_merge_kernel, dim3(ntok * H), dim3(128), 0, stream, (const float*)part, (bf16*)out, ldo, H,
               ksplits);

@@ -941,7 +941,7 @@ def latent_attention_mma(qa, out, heads, rank, rd, cache, page_table, page_size,
     defines = (("GB_LATENT_RANK", rank), ("GB_LATENT_ROT", rd))
     part = None
     if ksplits > 1:
-        need = ntok * heads * ksplits * (2 + rank)
+        need = ntok * heads * ksplits * (rank + 4)
         part = _latent_scratch.get(qa.device.index)
         if part is None or part.numel() < need:
             if part is not None:
