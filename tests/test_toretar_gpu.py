@@ -145,7 +145,7 @@ def _plain_latent_attention(qa, rows_of_seq, pos, seq, heads, rank, rd, window=N
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,rank,rd", [(3, 36, 6), (6, 128, 16), (1, 64, 32), (17, 48, 16), (4, 256, 32), (2, 512, 64)])
+@pytest.mark.parametrize("heads,rank,rd", [(3, 36, 6), (7, 112, 16), (1, 64, 32), (17, 48, 16), (4, 256, 32), (2, 512, 64)])
 @pytest.mark.parametrize("decoding", [False, True], ids=["prompt", "decoding"])
 def test_attention_over_latents_finds_planted_keys(dtype, heads, rank, rd, decoding):
     """Sequences of several pages in shuffled pages.  Every query is made to point at one key, the

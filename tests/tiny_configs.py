@@ -93,7 +93,7 @@ TORETAR_A = {
 TORETAR_B = {
     "architecture": "Toretar", "vocab": 520, "width": 128, "norm": {"eps": 1e-6},
     "layers": [
-        _toretar_layer(4, 32, 16, 48, 64, 0.144, 250000.0, 16, _toretar_moe(6, 3, 64, 1.0, {"ff": 96, "limit": 2.0})),
+        _toretar_layer(4, 48, 16, 40, 64, 0.125, 500000.0, 16, _toretar_moe(6, 3, 64, 1.1, {"ff": 80, "limit": 1.9})),
         _toretar_layer(1, 64, 32, 64, 96, 0.1, 10000.0, 32, _toretar_moe(2, 2, 32, 1.2, {"ff": 32, "limit": 0.9})),
         _toretar_layer(9, 16, 16, 32, 128, 0.177, 1000000.0, 16, _toretar_moe(8, 2, 48, 3.0, {"ff": 64, "limit": 1.0})),
     ],
