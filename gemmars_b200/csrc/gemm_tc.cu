@@ -793,12 +793,31 @@ struct TileWalk {
 // short inner dimensions (2,560: 16 us of MMAs a tile) it, not the MMAs, set the product's time.
 constexpr int PERSISTENT_QKV_THREADS = 320, QKV_STAGING_BYTES = 65 * 1024;   // pieces 32 KB, exchange 2 x 16 KB, sums 1 KB
 
+// A grouped product (the experts of a routed feed-forward): the rows of x are ordered by group and
+// every group's rows start at a multiple of the tile's tokens, so a tile of tokens belongs to one
+// group; tile_expert[m tile] names it (-1: a tile no group uses, which every role skips) and the
+// tile's rows of W are the group's (W stacks the groups' matrices, rows_per_expert each).  The gated
+// mode then applies g = min(g, limit), u = clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + shift)
+// when limit > 0, and multiplies row r of the result by row_scale[r].
+struct Grouped {
+  const int* tile_expert = nullptr;
+  const float* row_scale = nullptr;
+  int rows_per_expert = 0;
+  float limit = 0.f, alpha = 0.f, shift = 0.f;
+};
+__device__ __forceinline__ float clamped_gate(float g, float u, const Grouped& grp) {
+  g = fminf(g, grp.limit);
+  u = fminf(fmaxf(u, -grp.limit), grp.limit);
+  return __fdividef(g, 1.0f + __expf(-grp.alpha * g)) * (u + grp.shift);
+}
+
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(MODE == EPI_QKV_BF16 ? PERSISTENT_QKV_THREADS : THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                           const __grid_constant__ CUtensorMap map_y, int y_tma, const float* __restrict__ bias,
                           void* __restrict__ y, int M, int N, int K, long long ldy, int bn,
-                          const __grid_constant__ QkvTail tail, int split_last, int* __restrict__ part_flags) {
+                          const __grid_constant__ QkvTail tail, int split_last, int* __restrict__ part_flags,
+                          const __grid_constant__ Grouped grp) {
   constexpr bool GATED = MODE == EPI_SWIGLU_BF16;   // rows of a tile: 16 gate, 16 up, ... (see gate_rows)
   // the last round's tiles in parts along the inner dimension: only where parts can be added
   const int split = MODE == EPI_ACCUMULATE_F32 ? max(split_last, 1) : 1;
@@ -865,6 +884,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       for (TileWalk w(tiles, kb_total, split); w.more() && ok; w.next()) {
         int m0, n0;
         tile_origin(w.t, tiles_m, tiles_n, bn, TILE_F, m0, n0);
+        int w0 = n0;                                   // the tile's first row of W
+        if (grp.tile_expert) {
+          const int e = grp.tile_expert[m0 / bn];
+          if (e < 0) continue;
+          w0 += e * grp.rows_per_expert;
+        }
         for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1)) {
@@ -877,10 +902,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
           if (GATED) {   // map_w is cut into boxes of 64 rows: the gate rows, then the same features' up rows
             // (a request costs the issuing thread about 75 cycles: boxes of 16 rows, which would let a
             // warp gate without shared memory, made nine requests a block and the producer the limit)
-            tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[s]);
-            tma_load_2d(a + A_BYTES / 2, &map_w, kb * BK, N + n0, &full_bar[s]);
+            tma_load_2d(a, &map_w, kb * BK, w0, &full_bar[s]);
+            tma_load_2d(a + A_BYTES / 2, &map_w, kb * BK, N + w0, &full_bar[s]);
           } else {
-            tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[s]);
+            tma_load_2d(a, &map_w, kb * BK, w0, &full_bar[s]);
           }
           tma_load_2d(a + A_BYTES, &map_x, kb * BK, m0, &full_bar[s]);
         }
@@ -894,6 +919,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       uint32_t it = 0, i = 0;
       bool ok = true;
       for (TileWalk w(tiles, kb_total, split); w.more() && ok; w.next(), ++i) {
+        if (grp.tile_expert) {                         // a tile no group uses: not counted, as in the other roles
+          int m0, n0;
+          tile_origin(w.t, tiles_m, tiles_n, bn, TILE_F, m0, n0);
+          if (grp.tile_expert[m0 / bn] < 0) {
+            --i;
+            continue;
+          }
+        }
         const uint32_t b = i & 1;
         if (i >= 2 && !mbar_wait(&acc_empty[b], ((i >> 1) - 1) & 1)) {   // the epilogue has read this buffer out
           atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
@@ -933,9 +966,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     const bool both = bn % 32 == 0;   // 32 tokens per round; the result's map is cut to match
     uint32_t i = 0;
     for (TileWalk w(tiles, kb_total, split); w.more(); w.next(), ++i) {
-      const uint32_t b = i & 1;
       int m0, n0;
       tile_origin(w.t, tiles_m, tiles_n, bn, TILE_F, m0, n0);
+      if (grp.tile_expert && grp.tile_expert[m0 / bn] < 0) {
+        --i;
+        continue;
+      }
+      const uint32_t b = i & 1;
       const int n = n0 + f;
       bool have = __all_sync(0xffffffffu, mbar_wait(&acc_full[b], (i >> 1) & 1));
       if (!have && lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
@@ -985,6 +1022,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             float r[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) r[j] = silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j]));
+            if (grp.limit > 0.f) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r[j] = clamped_gate(__uint_as_float(g[j]), __uint_as_float(u[j]), grp);
+            }
+            if (grp.row_scale) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r[j] *= row + j < M ? grp.row_scale[row + j] : 0.f;
+            }
             if (y_tma) {
               uint8_t* p = tile_out.next(lane);
 #pragma unroll
@@ -1145,7 +1190,7 @@ int launch_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, const Ou
 template <int BN, int STAGES, int MODE>
 int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap& my, const float* bias, void* y, int M,
                       int N, int K, long long ldy, int bn, int ctas, cudaStream_t stream, const QkvTail& tail = QkvTail{},
-                      int* part_flags = nullptr) {
+                      int* part_flags = nullptr, const Grouped& grp = Grouped{}) {
   // stages, 1 KB of barriers, the pieces on their way out, 1 KB to align the base
   constexpr size_t STAGING = MODE == EPI_QKV_BF16 ? QKV_STAGING_BYTES : OUT_STAGING_BYTES;
   constexpr size_t SMEM = (size_t)STAGES * ((size_t)BM * BK * 2 + BN * BK * 2) + 1024 + STAGING + 1024;
@@ -1183,7 +1228,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap
     if (split > 1) grid = last * split < ctas && tiles < ctas ? last * split : ctas;
   }
   gb_launch(kernel, dim3(grid), dim3(NTHREADS), SMEM, stream, mw, mx, my.map, my.usable, bias, y, M, N, K, ldy, bn, tail,
-            split, part_flags);
+            split, part_flags, grp);
   return gb_launch_status();
 }
 
@@ -1336,6 +1381,36 @@ GB_EXPORT int gb_gemm_tc_persistent(const void* x, const void* w, const float* b
     }
   }
   return GB_ERR_ARG;
+}
+
+// The grouped form of gb_gemm_tc_persistent (see struct Grouped): x [M, K] holds the groups' rows one
+// group after the other, each group starting at a multiple of bn rows (M counts the padding);
+// w stacks `experts` matrices of N rows (2 N gated: gate rows, then up rows); tile_expert [M / bn].
+// mode 1: y float32 [M, N] = x W_g^T; mode 3: y bfloat16 [M, N] = row_scale * act(gate, up), act the
+// clamped form when limit > 0.  bn: 128 or 256.
+GB_EXPORT int gb_gemm_tc_grouped(const void* x, const void* w, void* y, int mode, int M, int N, int K, long long ldx,
+                                 long long ldy, int bn, int ctas, int experts, const int* tile_expert, const float* row_scale,
+                                 float limit, float alpha, float shift, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || experts <= 0) return 0;
+  if (K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ctas <= 0) return GB_ERR_SIZE;
+  if ((bn != 128 && bn != 256) || M % bn || !tile_expert) return GB_ERR_SIZE;
+  const bool gated = mode == EPI_SWIGLU_BF16;
+  if (!gated && mode != EPI_STORE_F32) return GB_ERR_ARG;
+  Grouped grp;
+  grp.tile_expert = tile_expert;
+  grp.row_scale = gated ? row_scale : nullptr;
+  grp.rows_per_expert = N * (gated ? 2 : 1);
+  grp.limit = limit; grp.alpha = alpha; grp.shift = shift;
+  CUtensorMap mw, mx;
+  if (!tensor_map(&mw, w, (uint64_t)experts * grp.rows_per_expert, (uint64_t)K, (uint64_t)K * 2, gated ? BM / 2 : BM)) return GB_ERR_ARG;
+  if (!tensor_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn)) return GB_ERR_ARG;
+  const OutMap my = out_map(y, mode, M, N, ldy, gated ? 16 : bn);
+  if (gated) {
+    if (bn > 128) return launch_persistent<256, 4, EPI_SWIGLU_BF16>(mw, mx, my, nullptr, y, M, N, K, ldy, bn, ctas, stream, QkvTail{}, nullptr, grp);
+    return launch_persistent<128, 6, EPI_SWIGLU_BF16>(mw, mx, my, nullptr, y, M, N, K, ldy, bn, ctas, stream, QkvTail{}, nullptr, grp);
+  }
+  if (bn > 128) return launch_persistent<256, 4, EPI_STORE_F32>(mw, mx, my, nullptr, y, M, N, K, ldy, bn, ctas, stream, QkvTail{}, nullptr, grp);
+  return launch_persistent<128, 6, EPI_STORE_F32>(mw, mx, my, nullptr, y, M, N, K, ldy, bn, ctas, stream, QkvTail{}, nullptr, grp);
 }
 
 // (cos, sin) of every packed token's angles: table [ntok][half] float2, for gb_gemm_tc_qkv_prompt.

@@ -6,7 +6,9 @@
 //    gathered by token, W_g is the expert's matrix.  The gate/up product applies the experts'
 //    activation in its epilogue (the tile interleaves 8 gate rows with the 8 up rows of the same
 //    features, so a thread holds both); the down product scales each row by its routing weight and
-//    leaves float32 rows that gb_moe_combine adds into the residual in slot order.
+//    leaves float32 rows that gb_moe_combine adds into the residual in slot order.  (Prompt steps
+//    run the same two products on the tcgen05 kernel of gemm_tc.cu instead, from a copy of the
+//    activations in a padded order: gb_moe_sort_padded, gb_moe_permute.)
 //  * the per-head products of latent attention: group = head, every group has all the tokens,
 //    A and C rows are a token's slice of a wider row, with an optional scale per (token, head).
 //
@@ -215,6 +217,61 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
   }
 }
 
+// As moe_sort_kernel, for the tcgen05 product that wants every expert's rows to start at a multiple
+// of `bn` rows: place[entry] is the entry's row in that padded order, row_entry[row] the entry of a
+// row (-1: padding), tile_expert[row / bn] the expert a tile of bn rows belongs to (-1: none).
+__global__ void __launch_bounds__(1024) moe_sort_padded_kernel(const int* __restrict__ idx, int entries, int E, int bn,
+                                                               int rows, int* __restrict__ tile_expert,
+                                                               int* __restrict__ place, int* __restrict__ row_entry) {
+  extern __shared__ int counts[];   // [E] counts, then [E] running starts
+  pdl_release_next();
+  pdl_wait_prior();
+  int* starts = counts + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  for (int r = threadIdx.x; r < rows; r += blockDim.x) row_entry[r] = -1;
+  for (int t = threadIdx.x; t < rows / bn; t += blockDim.x) tile_expert[t] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) atomicAdd(&counts[idx[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) {
+      starts[e] = acc;
+      const int tiles = (counts[e] + bn - 1) / bn;
+      for (int t = 0; t < tiles; ++t) tile_expert[acc / bn + t] = e;
+      acc += tiles * bn;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int at = atomicAdd(&starts[idx[i]], 1);
+    place[i] = at;
+    row_entry[at] = i;
+  }
+}
+
+// The activations in the padded order: row r = h[token of its entry], zeros for padding inside a used
+// tile (tiles that no expert uses are never read); scale[r] = the entry's routing weight.
+__global__ void __launch_bounds__(128) moe_permute_kernel(const bf16* __restrict__ h, long long ldh,
+                                                          const int* __restrict__ row_entry, const int* __restrict__ tile_expert,
+                                                          const float* __restrict__ wts, bf16* __restrict__ xp,
+                                                          float* __restrict__ scale, int width, int top, int bn) {
+  pdl_release_next();
+  pdl_wait_prior();
+  const int r = blockIdx.x;
+  if (tile_expert[r / bn] < 0) return;
+  const int e = row_entry[r];
+  uint4* dst = (uint4*)(xp + (size_t)r * width);
+  if (e < 0) {
+    for (int i = threadIdx.x; i < width / 8; i += 128) dst[i] = make_uint4(0, 0, 0, 0);
+    if (threadIdx.x == 0) scale[r] = 0.f;
+    return;
+  }
+  const uint4* src = (const uint4*)(h + (size_t)(e / top) * ldh);
+  for (int i = threadIdx.x; i < width / 8; i += 128) dst[i] = src[i];
+  if (threadIdx.x == 0) scale[r] = wts[e];
+}
+
 // residual[t] += sum over the token's slots, in slot order, of the rows the down product left
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ place,
                                                           float* __restrict__ residual, long long ldr, int width, int top) {
@@ -283,6 +340,25 @@ GB_EXPORT int gb_moe_sort(const int* idx, int entries, int E, int* offsets, int*
   if (entries <= 0) return 0;
   if (E <= 0 || E > 4096) return GB_ERR_SIZE;
   gb_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, idx, entries, E, offsets, perm, place);
+  return gb_launch_status();
+}
+
+GB_EXPORT int gb_moe_sort_padded(const int* idx, int entries, int E, int bn, int rows, int* tile_expert, int* place,
+                                 int* row_entry, cudaStream_t stream) {
+  if (entries <= 0) return 0;
+  if (E <= 0 || E > 4096 || bn <= 0 || rows % bn || rows < entries + E * (bn - 1)) return GB_ERR_SIZE;
+  gb_launch(moe_sort_padded_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, idx, entries, E, bn, rows,
+            tile_expert, place, row_entry);
+  return gb_launch_status();
+}
+
+// h: [ntok, width] bfloat16 rows ldh apart (width % 8 == 0, 16-byte aligned rows); xp: [rows, width]
+GB_EXPORT int gb_moe_permute(const void* h, long long ldh, const int* row_entry, const int* tile_expert, const float* wts,
+                             void* xp, float* scale, int rows, int width, int top, int bn, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (width % 8 || ldh % 8 || ((uintptr_t)h & 15) || ((uintptr_t)xp & 15)) return GB_ERR_SIZE;
+  gb_launch(moe_permute_kernel, dim3(rows), dim3(128), 0, stream, (const bf16*)h, ldh, row_entry, tile_expert, wts, (bf16*)xp,
+            scale, width, top, bn);
   return gb_launch_status();
 }
 

@@ -1079,15 +1079,85 @@ def moe_experts_grouped(h, idx, wts, sg, w_gate_up, w_down, shared_gate_up, shar
     f = _fn("grouped_gemm", "gb_moe_combine", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p])
     _check(f(rows.data_ptr(), place.data_ptr(), residual.data_ptr(), residual.stride(0), t, width, top, _stream()),
            "moe_combine", "elementwise", _nbytes(rows) + 2 * t * width * 4)
-    if shared_down is not None:
-        ffs = shared_down.shape[1]
-        gu = torch.empty((t, 2 * ffs), dtype=torch.bfloat16, device=h.device)
-        gemm(h, shared_gate_up, gu)
-        ys = torch.empty((t, ffs), dtype=torch.bfloat16, device=h.device)
-        f = _fn("grouped_gemm", "gb_gated_act", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_void_p])
-        _check(f(gu.data_ptr(), ys.data_ptr(), _ptr(sg), t, ffs, shared_limit, alpha, shift, _stream()), "gated_act",
-               "elementwise", _nbytes(gu, ys))
-        gemm(ys, shared_down, residual, accumulate=True)
+    _shared_expert(h, sg, shared_gate_up, shared_down, residual, shared_limit, alpha, shift)
+
+
+MOE_TC_MIN_TOKENS = 256
+MOE_TC_TILE = 128
+
+
+def moe_tc_usable(h, w_gate_up, w_down) -> bool:
+    """Whether a step's experts run on the tcgen05 product: a prompt's worth of tokens, operands the
+    product's TMA loads can address."""
+    return (moe_grouped_usable(h, w_gate_up, w_down) and h.shape[0] >= MOE_TC_MIN_TOKENS
+            and w_gate_up.data_ptr() % 16 == 0 and w_down.data_ptr() % 16 == 0)
+
+
+def gemm_tc_grouped(x, w, y, n, experts, tile_expert, row_scale=None, gated=False, limit=0.0, alpha=0.0, shift=0.0,
+                    bn=MOE_TC_TILE):
+    """The tcgen05 product over groups of rows: x [rows, K] holds the groups one after the other, each
+    starting at a multiple of ``bn`` rows; w stacks the groups' matrices ([experts * n, K], or
+    [experts * 2 n, K] gated); tile_expert names the group of every tile of ``bn`` rows (-1: none).
+    y float32 [rows, n], or with ``gated`` bfloat16 [rows, n] = row_scale * act(gate, up)."""
+    _cuda(x, w, y, tile_expert, row_scale)
+    rows, k = x.shape
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous()
+    assert y.shape == (rows, n) and y.is_contiguous() and y.dtype == (torch.bfloat16 if gated else torch.float32)
+    assert tile_expert.dtype == torch.int32 and tile_expert.numel() == rows // bn and rows % bn == 0
+    f = _fn("gemm_tc", "gb_gemm_tc_grouped",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p,
+             c_void_p, c_float, c_float, c_float, c_void_p])
+    _check(f(x.data_ptr(), w.data_ptr(), y.data_ptr(), 3 if gated else 1, rows, n, k, x.stride(0), y.stride(0), bn,
+             sm_count(x.device), experts, tile_expert.data_ptr(), _ptr(row_scale), limit, alpha, shift, _stream()),
+           "gemm_tc_grouped", "matmul", _nbytes(x, w, y))
+
+
+def moe_experts_tc(h, idx, wts, sg, w_gate_up, w_down, shared_gate_up, shared_down, residual, limit, shared_limit, alpha,
+                   shift):
+    """As moe_experts_grouped for a prompt step, the experts' two products on the tcgen05 kernel: the
+    activations are copied into an order in which every expert's rows start at a multiple of the
+    tile's tokens (zeros between), the routing weight multiplies the activation's rows, and a token's
+    float32 rows are added into the residual in slot order."""
+    _cuda(h, idx, wts, sg, w_gate_up, w_down, shared_gate_up, shared_down, residual)
+    t, width = h.shape
+    e, ff2, _ = w_gate_up.shape
+    ff, top, bn = ff2 // 2, idx.shape[1], MOE_TC_TILE
+    entries = t * top
+    rows = (-(-entries // bn) + e) * bn
+    meta = torch.empty(rows // bn + entries + rows, dtype=torch.int32, device=h.device)
+    tile_expert, place, row_entry = meta[:rows // bn], meta[rows // bn:rows // bn + entries], meta[rows // bn + entries:]
+    f = _fn("grouped_gemm", "gb_moe_sort_padded", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(idx.data_ptr(), entries, e, bn, rows, tile_expert.data_ptr(), place.data_ptr(), row_entry.data_ptr(), _stream()),
+           "moe_sort", "elementwise", 3 * entries * 4)
+    xp = torch.empty((rows, width), dtype=torch.bfloat16, device=h.device)
+    scale = torch.empty((rows,), dtype=torch.float32, device=h.device)
+    f = _fn("grouped_gemm", "gb_moe_permute", [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                               c_int, c_int, c_int, c_void_p])
+    _check(f(h.data_ptr(), h.stride(0), row_entry.data_ptr(), tile_expert.data_ptr(), wts.data_ptr(), xp.data_ptr(),
+             scale.data_ptr(), rows, width, top, bn, _stream()), "moe_permute", "elementwise", 2 * entries * width * 2)
+    y = torch.empty((rows, ff), dtype=torch.bfloat16, device=h.device)
+    gemm_tc_grouped(xp, w_gate_up.view(e * ff2, width), y, ff, e, tile_expert, scale, gated=True, limit=limit, alpha=alpha,
+                    shift=shift)
+    out = torch.empty((rows, width), dtype=torch.float32, device=h.device)
+    gemm_tc_grouped(y, w_down.view(e * width, ff), out, width, e, tile_expert)
+    f = _fn("grouped_gemm", "gb_moe_combine", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p])
+    _check(f(out.data_ptr(), place.data_ptr(), residual.data_ptr(), residual.stride(0), t, width, top, _stream()),
+           "moe_combine", "elementwise", entries * width * 4 + 2 * t * width * 4)
+    _shared_expert(h, sg, shared_gate_up, shared_down, residual, shared_limit, alpha, shift)
+
+
+def _shared_expert(h, sg, shared_gate_up, shared_down, residual, shared_limit, alpha, shift):
+    """residual += sg * shared(h): two dense products of the framework's around the activation."""
+    if shared_down is None:
+        return
+    t, ffs = h.shape[0], shared_down.shape[1]
+    gu = torch.empty((t, 2 * ffs), dtype=torch.bfloat16, device=h.device)
+    gemm(h, shared_gate_up, gu)
+    ys = torch.empty((t, ffs), dtype=torch.bfloat16, device=h.device)
+    f = _fn("grouped_gemm", "gb_gated_act", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_void_p])
+    _check(f(gu.data_ptr(), ys.data_ptr(), _ptr(sg), t, ffs, shared_limit, alpha, shift, _stream()), "gated_act",
+           "elementwise", _nbytes(gu, ys))
+    gemm(ys, shared_down, residual, accumulate=True)
 
 
 # --------------------------------------------------------------------------- sampling

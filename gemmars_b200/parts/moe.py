@@ -101,7 +101,12 @@ class RoutedExperts(Part):
         idx, wts, sg = self._route(h)
         if self.shared_ff and sg is None:
             sg = torch.ones((h.shape[0],), dtype=torch.float32, device=h.device)
-        run = kernels.moe_experts_grouped if kernels.moe_grouped_usable(h, self.gate_up, self.down) else kernels.moe_experts
+        if kernels.moe_tc_usable(h, self.gate_up, self.down):
+            run = kernels.moe_experts_tc
+        elif kernels.moe_grouped_usable(h, self.gate_up, self.down):
+            run = kernels.moe_experts_grouped
+        else:
+            run = kernels.moe_experts
         run(h, idx, wts, sg, self.gate_up, self.down, self.shared_gate_up, self.shared_down, residual,
                             self.limit, self.shared_limit, self.alpha, self.shift)
 

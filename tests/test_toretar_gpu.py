@@ -21,7 +21,7 @@ TOL_BF16 = 1.5e-2
 PAGE = 64
 
 
-def _judge(errors, tol, dtype, what):
+def _within(errors, tol, dtype, what):
     """float32: every position within ``tol``.  bfloat16: rounding the router's input moves a token
     whose two candidate experts have nearly equal logits to the other expert now and then, which
     changes that position's logits by far more than rounding; random weights have such tokens, so up
@@ -235,7 +235,8 @@ def test_expert_choice_from_the_logits(t, experts, top):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("t,width,experts,top,ff,ffs", [(9, 72, 5, 2, 40, 56), (200, 128, 6, 3, 64, 96), (2, 40, 3, 1, 24, 0),
-                                                      (130, 64, 2, 2, 32, 16)])
+                                                      (130, 64, 2, 2, 32, 16), (300, 128, 6, 3, 64, 96),
+                                                      (700, 64, 40, 1, 72, 0), (257, 256, 3, 2, 200, 136)])
 def test_routed_feed_forward(dtype, t, width, experts, top, ff, ffs):
     """The whole feed-forward part against the plain one; inputs large enough that both clamps act."""
     from gemmars_b200.parts.base import build_part
@@ -324,7 +325,7 @@ def test_all_cuttings_match_the_plain_implementation(name, dtype, models, tmp_pa
     scale = max(float(np.abs(r).max()) for r in ref)
     tol = (TOL_F32 if dtype == "float32" else TOL_BF16) * scale
     for tag in "wtb":
-        _judge([np.abs(got[(f"{tag}{i}", p)] - r[p]).max() for i, r in enumerate(ref) for p in range(len(r))], tol, dtype,
+        _within([np.abs(got[(f"{tag}{i}", p)] - r[p]).max() for i, r in enumerate(ref) for p in range(len(r))], tol, dtype,
                f"cutting {tag!r}")
     if dtype == "float32":
         for i, r in enumerate(ref):
@@ -351,7 +352,7 @@ def test_residual_after_every_layer(dtype, models):
     assert len(seen) == len(want)
     for i, (a, b) in enumerate(zip(seen, want)):
         tol = (1e-5 if dtype == "float32" else 2e-2) * np.abs(b).max()
-        _judge(np.abs(a - b).max(axis=1), tol, dtype, f"layer {i}")
+        _within(np.abs(a - b).max(axis=1), tol, dtype, f"layer {i}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -397,9 +398,9 @@ def test_portions_long_decoding_and_reused_slots(dtype, models):
                 c = None
         runner.close(b)
         assert runner.cache.pages_held() == 0
-        _judge([np.abs(got[("a", p)] - ref[4][p]).max() for p in range(len(reqs[4]))], tol, dtype, "portions")
-        _judge([np.abs(got[("b", p)] - long_ref[p]).max() for p in range(len(long_toks))], tol, dtype, "decoded")
-        _judge([np.abs(got[("c", p)] - ref[0][p]).max() for p in range(len(reqs[0]))], tol, dtype, "neighbour")
+        _within([np.abs(got[("a", p)] - ref[4][p]).max() for p in range(len(reqs[4]))], tol, dtype, "portions")
+        _within([np.abs(got[("b", p)] - long_ref[p]).max() for p in range(len(long_toks))], tol, dtype, "decoded")
+        _within([np.abs(got[("c", p)] - ref[0][p]).max() for p in range(len(reqs[0]))], tol, dtype, "neighbour")
         if first_round is None:
             first_round = got
         elif dtype == "float32":
@@ -421,7 +422,7 @@ def test_greedy_generation_through_the_engine(models):
     again = eng.generate(list(reversed(prompts)), max_tokens=10, stop_ids=stop)
     assert [r.tokens for r in reversed(again)] == [r.tokens for r in res]
     # bfloat16 decodes through captured steps: the tokens it picks are the plain model's best or within
-    # rounding of it (but for the few that follow a token routed to another expert, see _judge)
+    # rounding of it (but for the few that follow a token routed to another expert, see _within)
     eng16 = Engine.load(folder, "dtype=bfloat16;max_batch=4;max_tokens=2048")
     near, total = 0, 0
     for p, r in zip(prompts, eng16.generate(prompts, max_tokens=8, stop_ids=[])):
