@@ -36,7 +36,8 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(
     const float* __restrict__ inv_freq, int rot, float q_scale, T* __restrict__ q_nope, long long ldqn,
     T* __restrict__ q_lat, long long ldql, float* __restrict__ gate, T* __restrict__ cache,
     const int* __restrict__ page_table, int table_width, int page_size, const int* __restrict__ tok_pos,
-    const int* __restrict__ tok_seq, const int* __restrict__ seq_slot, int H, int dim, int rd, int rank) {
+    const int* __restrict__ tok_seq, const int* __restrict__ seq_slot, int H, int dim, int rd, int rank,
+    T* __restrict__ dense, long long ldd) {
   __shared__ float scratch[34];
   pdl_release_next();
   pdl_wait_prior();
@@ -49,10 +50,18 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(
   for (int i = tid; i < rank; i += blockDim.x) ss = fmaf(kv[i], kv[i], ss);
   ss = block_sum(ss, scratch);
   const float rstd = 1.0f / sqrtf(ss / (float)rank + eps);
-  if (cache != nullptr) {
-    const int slot = seq_slot[tok_seq[t]];
-    const int page = page_table[(size_t)slot * table_width + (pos / page_size) % table_width];
-    T* row = cache + ((size_t)page * page_size + pos % page_size) * (size_t)(rank + rd);
+  // the row goes into the paged cache and, when asked for, into a dense copy [ntok, rank + rd] as well
+  for (int copy = 0; copy < 2; ++copy) {
+    T* row;
+    if (copy == 0) {
+      if (cache == nullptr) continue;
+      const int slot = seq_slot[tok_seq[t]];
+      const int page = page_table[(size_t)slot * table_width + (pos / page_size) % table_width];
+      row = cache + ((size_t)page * page_size + pos % page_size) * (size_t)(rank + rd);
+    } else {
+      if (dense == nullptr) continue;
+      row = dense + (size_t)t * ldd;
+    }
     for (int i = tid; i < rank; i += blockDim.x) row[i] = from_f32<T>(kv[i] * rstd * norm_w[i]);
     // the shared rotated key part: pairs below `rot` turn, the rest passes
     for (int i = tid; i < rd / 2 + (rd & 1); i += blockDim.x) {
@@ -100,14 +109,14 @@ GB_EXPORT int gb_latent_prepare(const float* q_in, long long ldq, const float* k
                                 float q_scale, void* q_nope, long long ldqn, void* q_lat, long long ldql, float* gate,
                                 void* cache, int dtype, const int* page_table, int table_width, int page_size,
                                 const int* tok_pos, const int* tok_seq, const int* seq_slot, int ntok, int H, int dim,
-                                int rd, int rank, cudaStream_t stream) {
+                                int rd, int rank, void* dense, long long ldd, cudaStream_t stream) {
   if (ntok <= 0) return 0;
   if (H <= 0 || dim < 0 || rd < 0 || rank <= 0 || rot < 0 || rot > rd || (rot & 1)) return GB_ERR_SIZE;
   if (rot > 0 && inv_freq == nullptr) return GB_ERR_ARG;
 #define LAUNCH(T)                                                                                                     \
   gb_launch(latent_prepare_kernel<T>, dim3(ntok), dim3(256), 0, stream, q_in, ldq, kv_in, ldkv, g_in, ldg, norm_w, eps, \
             inv_freq, rot, q_scale, (T*)q_nope, ldqn, (T*)q_lat, ldql, gate, (T*)cache, page_table, table_width,       \
-            page_size, tok_pos, tok_seq, seq_slot, H, dim, rd, rank)
+            page_size, tok_pos, tok_seq, seq_slot, H, dim, rd, rank, (T*)dense, ldd)
   if (dtype == GB_F32) LAUNCH(float);
   else if (dtype == GB_BF16) LAUNCH(bf16);
   else return GB_ERR_DTYPE;

@@ -67,7 +67,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, long long ldq, bf16* __
                             float* __restrict__ part, const bf16* __restrict__ cache, const int* __restrict__ page_table,
                             int table_width, int page_size, const int* __restrict__ cu_seqlens,
                             const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int n_seqs, int H,
-                            int window, int ksplits) {
+                            int window, int ksplits, long long head_stride, const float* __restrict__ out_scale) {
   constexpr int NB = KEYS / 8;                         // blocks of 8 keys a tile
   constexpr int SXP = KEYS + 4;                        // pitch of the exchanged scores
   static_assert(NB % 2 == 0, "key blocks come in pairs");
@@ -80,6 +80,8 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, long long ldq, bf16* __
   bf16* Qs = Ks;                                      // [tile_rows][LDS], before the first key tile
   float* Sx = (float*)(Ks + 2 * KEYS * LDS);          // [groups][NSPLIT][16][SXP], only with NSPLIT > 1
   // ---- which sequence and which tile of its rows
+  const int heads_all = H;
+  if (head_stride > 0) H = 1;                          // see per_head below
   int b = 0, tile = blockIdx.x, rows_b = 0;
   for (; b < n_seqs; ++b) {
     rows_b = (cu_seqlens[b + 1] - cu_seqlens[b]) * H;
@@ -93,6 +95,16 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, long long ldq, bf16* __
   const int rg = warp / NSPLIT, w = warp % NSPLIT;
   const int slot = seq_slot[b], start = seq_start[b], tok_base = cu_seqlens[b];
   const int row_base = tile * tile_rows;
+  // head_stride > 0: every head has rows of its own (keys and values expanded per head), head
+  // blockIdx.z's at cache + z * head_stride, a sequence's rows contiguous from its first packed token
+  // (all sequences start at position 0); the rows of a tile are then tokens of that one head
+  const bool per_head = head_stride > 0;
+  const int hz = per_head ? (int)blockIdx.z : 0;
+  if (per_head) {
+    qa += (size_t)hz * KD;
+    out += (size_t)hz * RANK;
+    cache += (size_t)hz * head_stride;
+  }
   // ---- the keys this CTA reads
   const int first_tok = row_base / H;
   const int last_tok = (min(rows_b, row_base + tile_rows) - 1) / H;
@@ -118,8 +130,13 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, long long ldq, bf16* __
   }
   auto load_keys = [&](int t, int stage) {
     const int key0 = t * KEYS;
-    const int page = page_table[(size_t)slot * table_width + (key0 / page_size) % table_width];
-    const bf16* src = cache + ((size_t)page * page_size + key0 % page_size) * KD;
+    const bf16* src;
+    if (per_head) {
+      src = cache + (size_t)(tok_base + key0) * KD;
+    } else {
+      const int page = page_table[(size_t)slot * table_width + (key0 / page_size) % table_width];
+      src = cache + ((size_t)page * page_size + key0 % page_size) * KD;
+    }
     bf16* dst = Ks + (size_t)stage * KEYS * LDS;
     for (int e = tid; e < KEYS * CH; e += blockDim.x) {
       const int r = e / CH, ch = e % CH;
@@ -251,7 +268,8 @@ latent_attention_mma_kernel(const bf16* __restrict__ qa, long long ldq, bf16* __
     for (int half = 0; half < 2; ++half) {
       const int row = half ? r1 : r0;
       if (!(half ? v1 : v0)) continue;
-      const float inv = 1.0f / (half ? l1 : l0);
+      float inv = 1.0f / (half ? l1 : l0);
+      if (out_scale) inv *= out_scale[(size_t)(tok_base + row / H) * heads_all + (per_head ? hz : row % H)];
       bf16* dst = out + (size_t)(tok_base + row / H) * ldo + (size_t)(row % H) * RANK + w * DW + 2 * c;
 #pragma unroll
       for (int d = 0; d < DW / 8; ++d) *(uint32_t*)(dst + d * 8) = pack_bf16(o[d][2 * half] * inv, o[d][2 * half + 1] * inv);
@@ -307,7 +325,8 @@ __global__ void __launch_bounds__(128) latent_attention_merge_kernel(const float
 template <int KEYS>
 int launch_latent(const bf16* qa, long long ldq, bf16* out, long long ldo, float* part, const bf16* cache, const int* page_table,
                   int table_width, int page_size, const int* cu_seqlens, const int* seq_start, const int* seq_slot, int n_seqs,
-                  int ntok, int H, int groups, int window, int ksplits, cudaStream_t stream) {
+                  int ntok, int H, int groups, int window, int ksplits, long long head_stride, const float* out_scale,
+                  cudaStream_t stream) {
   const int tile_rows = groups * 16;
   if (tile_rows > 2 * KEYS) return GB_ERR_SIZE;       // the queries are staged in the key buffers
   const size_t smem = 2 * (size_t)KEYS * LDS * sizeof(bf16) +
@@ -318,9 +337,11 @@ int launch_latent(const bf16* qa, long long ldq, bf16* out, long long ldo, float
       return GB_ERR_SIZE;
     allowed = smem;
   }
-  dim3 grid(((long long)ntok * H + tile_rows - 1) / tile_rows + n_seqs, ksplits);
+  const int row_heads = head_stride > 0 ? 1 : H;
+  dim3 grid(((long long)ntok * row_heads + tile_rows - 1) / tile_rows + n_seqs, ksplits, head_stride > 0 ? H : 1);
   gb_launch(latent_attention_mma_kernel<KEYS>, grid, dim3(groups * NSPLIT * 32), smem, stream, qa, ldq, out, ldo, part, cache,
-            page_table, table_width, page_size, cu_seqlens, seq_start, seq_slot, n_seqs, H, window, ksplits);
+            page_table, table_width, page_size, cu_seqlens, seq_start, seq_slot, n_seqs, H, window, ksplits, head_stride,
+            out_scale);
   return 0;
 }
 
@@ -334,25 +355,29 @@ GB_EXPORT long long gb_latent_attention_mma_scratch(int ntok, int H, int ksplits
 // out: [ntok, H * RANK]; cache: [pages, page_size, RANK + ROT]; seq_start: each sequence's length
 // before the step (the cache already holds the step's own rows); part: float32 scratch of
 // gb_latent_attention_mma_scratch() floats when ksplits > 1.  max_rows: the most rows (tokens * H)
-// one sequence brings, for the size of a CTA.
+// one sequence brings, for the size of a CTA.  head_stride > 0: the rows are per head and contiguous
+// (cache: [H][all packed tokens + a tile's worth][RANK + ROT], elements head_stride apart; every
+// sequence starts at position 0; no page table; ksplits 1).  out_scale: float32 [ntok, H] or null,
+// multiplied into the output (ksplits 1 only).
 GB_EXPORT int gb_latent_attention_mma(const void* qa, long long ldq, void* out, long long ldo, float* part,
                                       const void* cache, const int* page_table, int table_width, int page_size,
                                       const int* cu_seqlens, const int* seq_start, const int* seq_slot, int n_seqs,
                                       int ntok, int H, int rank, int rot, int max_rows, int window, int ksplits,
-                                      cudaStream_t stream) {
+                                      long long head_stride, const float* out_scale, cudaStream_t stream) {
   if (ntok <= 0 || n_seqs <= 0) return 0;
   if (rank != RANK || rot != ROT || H <= 0 || page_size % 64 || ksplits < 1 || ksplits > MAX_KSPLITS) return GB_ERR_SIZE;
   if (((uintptr_t)qa & 15) || (ldq % 8) || ((uintptr_t)out & 3) || (ldo % 2) || ((uintptr_t)cache & 15)) return GB_ERR_SIZE;
-  if (ksplits > 1 && (part == nullptr || ((uintptr_t)part & 15))) return GB_ERR_ARG;
+  if (ksplits > 1 && (part == nullptr || ((uintptr_t)part & 15) || head_stride > 0 || out_scale)) return GB_ERR_ARG;
+  if (head_stride > 0 && (H > 65535 || head_stride % 8)) return GB_ERR_SIZE;
   int groups = (max_rows + 15) / 16;
   groups = groups < 1 ? 1 : (groups > MAX_GROUPS ? MAX_GROUPS : groups);
   int rc;
   if (ksplits > 1)
     rc = launch_latent<32>((const bf16*)qa, ldq, (bf16*)out, ldo, part, (const bf16*)cache, page_table, table_width, page_size,
-                           cu_seqlens, seq_start, seq_slot, n_seqs, ntok, H, groups, window, ksplits, stream);
+                           cu_seqlens, seq_start, seq_slot, n_seqs, ntok, H, groups, window, ksplits, head_stride, out_scale, stream);
   else
     rc = launch_latent<64>((const bf16*)qa, ldq, (bf16*)out, ldo, part, (const bf16*)cache, page_table, table_width, page_size,
-                           cu_seqlens, seq_start, seq_slot, n_seqs, ntok, H, groups, window, ksplits, stream);
+                           cu_seqlens, seq_start, seq_slot, n_seqs, ntok, H, groups, window, ksplits, head_stride, out_scale, stream);
   if (rc) return rc;
   if (ksplits > 1)
     gb_launch(latent_attention_merge_kernel, dim3(ntok * H), dim3(128), 0, stream, (const float*)part, (bf16*)out, ldo, H,

@@ -806,13 +806,14 @@ def attention_prefill_tc_status(head_dim: int = 0, reset: bool = True) -> int:
 # --------------------------------------------------------------------------- latent attention
 
 def latent_prepare(q_in, kv_in, g_in, norm_w, eps, inv_freq, rot, q_scale, q_nope, q_lat, gate, cache, page_table,
-                   page_size, tok_pos, tok_seq, seq_slot, heads, dim, rd, rank):
+                   page_size, tok_pos, tok_seq, seq_slot, heads, dim, rd, rank, dense=None):
     """From the float32 projections of a latent attention layer: the cache row of every token
     (RMS-normed latent ``kv_in[:, :rank]``, then the key part ``kv_in[:, rank:]`` with its first
     ``rot`` dims rotated as interleaved pairs) into the paged ``cache`` [pages, page_size, rank + rd];
     the queries' unrotated dims times ``q_scale`` into ``q_nope`` [T, heads * dim], their rotated
     dims (rotated, scaled) into the last ``rd`` columns of each head of ``q_lat``
-    [T, heads * (rank + rd)]; ``gate`` [T, heads] = sigmoid(g_in) (float32; None: no gate)."""
+    [T, heads * (rank + rd)]; ``gate`` [T, heads] = sigmoid(g_in) (float32; None: no gate).  ``dense``
+    [T, rank + rd] (None: not wanted) receives the same rows as the cache, token by token."""
     _cuda(q_in, kv_in, g_in, norm_w, inv_freq, q_nope, q_lat, gate, cache, page_table, tok_pos, tok_seq, seq_slot)
     t = q_in.shape[0]
     assert q_in.dtype == torch.float32 and kv_in.dtype == torch.float32 and q_in.stride(1) == 1 and kv_in.stride(1) == 1
@@ -829,12 +830,15 @@ def latent_prepare(q_in, kv_in, g_in, norm_w, eps, inv_freq, rot, q_scale, q_nop
     f = _fn("latent_attention", "gb_latent_prepare",
             [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_int, c_float,
              c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
-             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p])
+    if dense is not None:
+        assert dense.dtype == q_lat.dtype and dense.shape == (t, rank + rd) and dense.stride(1) == 1
     _check(f(q_in.data_ptr(), q_in.stride(0), kv_in.data_ptr(), kv_in.stride(0), _ptr(g_in),
              g_in.stride(0) if g_in is not None else 0, norm_w.data_ptr(), eps, _ptr(inv_freq), rot, q_scale,
              q_nope.data_ptr(), q_nope.stride(0), q_lat.data_ptr(), q_lat.stride(0), _ptr(gate), _ptr(cache),
              dtype_code(q_lat.dtype), _ptr(page_table), page_table.shape[1] if page_table is not None else 1, page_size,
-             tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), t, heads, dim, rd, rank, _stream()),
+             tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), t, heads, dim, rd, rank, _ptr(dense),
+             dense.stride(0) if dense is not None else 0, _stream()),
            "latent_prepare", "elementwise", _nbytes(q_in, kv_in, q_nope) + t * (rank + 2 * rd) * q_lat.element_size())
 
 
@@ -928,16 +932,22 @@ _latent_scratch = {}
 
 
 def latent_attention_mma(qa, out, heads, rank, rd, cache, page_table, page_size, cu_seqlens, seq_start, seq_slot,
-                         max_new: int, window=None, ksplits: int = 1, cache_bytes: int = 0):
+                         max_new: int, window=None, ksplits: int = 1, cache_bytes: int = 0, head_stride: int = 0,
+                         out_scale=None):
     """bfloat16 latent attention on the tensor cores (mma.sync) for packed sequences that bring any
     number of tokens each; with ``ksplits`` > 1 the keys of a tile of rows are dealt to that many
-    CTAs and a second kernel adds their parts."""
-    _cuda(qa, out, cache, page_table, cu_seqlens, seq_start, seq_slot)
+    CTAs and a second kernel adds their parts.  ``head_stride`` > 0: every head has rows of its own,
+    ``cache`` [heads, packed tokens + 64, rank + rd] (elements ``head_stride`` apart), a sequence's rows
+    from its first packed token on, every sequence from position 0, no page table; ``out_scale``
+    float32 [T, heads] multiplies the output."""
+    _cuda(qa, out, cache, page_table, cu_seqlens, seq_start, seq_slot, out_scale)
     if not latent_attention_mma_usable(qa.dtype, rank, rd, page_size):
         raise KernelError(f"latent_attention_mma: latent {rank} + {rd}, pages of {page_size} or {qa.dtype} not supported")
     assert qa.stride(-1) == 1 and out.stride(-1) == 1 and out.dtype == cache.dtype == torch.bfloat16 and cache.is_contiguous()
     assert qa.shape[1] == heads * (rank + rd) and out.shape[1] == heads * rank and cache.shape[-1] == rank + rd
     ntok = qa.shape[0]
+    if head_stride:
+        assert ksplits == 1 and cache.shape[0] == heads and cache.shape[1] >= ntok + 64 and head_stride == cache.stride(0)
     defines = (("GB_LATENT_RANK", rank), ("GB_LATENT_ROT", rd))
     part = None
     if ksplits > 1:
@@ -949,10 +959,11 @@ def latent_attention_mma(qa, out, heads, rank, rd, cache, page_table, page_size,
             part = _latent_scratch[qa.device.index] = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=qa.device)
     f = _fn("latent_attention_mma", "gb_latent_attention_mma",
             [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
-             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p], defines=defines)
-    _check(f(qa.data_ptr(), qa.stride(0), out.data_ptr(), out.stride(0), _ptr(part), cache.data_ptr(), page_table.data_ptr(),
-             page_table.shape[1], page_size, cu_seqlens.data_ptr(), seq_start.data_ptr(), seq_slot.data_ptr(),
-             seq_slot.numel(), ntok, heads, rank, rd, max_new * heads, window or 0, ksplits, _stream()),
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p], defines=defines)
+    _check(f(qa.data_ptr(), qa.stride(0), out.data_ptr(), out.stride(0), _ptr(part), cache.data_ptr(), _ptr(page_table),
+             page_table.shape[1] if page_table is not None else 1, page_size, cu_seqlens.data_ptr(), seq_start.data_ptr(),
+             seq_slot.data_ptr(), seq_slot.numel(), ntok, heads, rank, rd, max_new * (1 if head_stride else heads),
+             window or 0, ksplits, head_stride, _ptr(out_scale), _stream()),
            "latent_attention_mma", "attention", _nbytes(qa, out) + cache_bytes)
     if ksplits > 1:
         count_launches(1)   # the merge kernel
@@ -983,10 +994,26 @@ def latent_attention(ctx, qa, out, heads, rank, rd, cache, page_table, page_size
                          window, cache_bytes=cached)
 
 
-def latent_attention_units(compute: str, rank: int, rd: int):
+# prompt steps of at least this many tokens whose sequences all start at position 0 expand keys and
+# values per head and run attention over heads of dim + rot_dim with values of vdim, instead of over
+# the latent rows: (2 rank + rot_dim) / (2 vdim + dim + rot_dim) times less arithmetic
+LATENT_EXPAND_MIN_TOKENS = 256
+
+
+def latent_expand_usable(dtype, rank: int, dim: int, rd: int, vd: int) -> bool:
+    """Whether a prompt step may run attention over expanded heads: the same kernel with the value
+    in front of the key ([v | k_nope | k_rot] rows, so vdim plays the latent and dim + rot_dim the
+    rest), rows the grouped product can write, and an expansion that saves arithmetic."""
+    return (latent_attention_mma_usable(dtype, vd, dim + rd, 64) and rank % 8 == 0 and rd % 8 == 0 and dim > 0
+            and 2 * vd + dim + rd < 2 * rank + rd)
+
+
+def latent_attention_units(compute: str, rank: int, rd: int, dim: int = 0, vd: int = 0):
     units = [("latent_attention", ())]
     if compute != "float32" and latent_attention_mma_usable(torch.bfloat16, rank, rd, 64):
         units.append(("latent_attention_mma", (("GB_LATENT_RANK", rank), ("GB_LATENT_ROT", rd))))
+    if compute != "float32" and vd and latent_expand_usable(torch.bfloat16, rank, dim, rd, vd):
+        units.append(("latent_attention_mma", (("GB_LATENT_RANK", vd), ("GB_LATENT_ROT", dim + rd))))
     return units
 
 

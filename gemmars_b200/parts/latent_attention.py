@@ -78,17 +78,19 @@ class LatentAttention(Part):
         # [heads, rank, dim]: the matrix that carries a head's unrotated query dims into the latent space
         self.uk_t = t["uk"].view(nh, self.dim, r).transpose(1, 2).contiguous()
         self.uv = t["uv"].view(nh, self.vdim, r).contiguous()
+        self.uk = t["uk"].view(nh, self.dim, r).contiguous()     # as stored: for prompts that expand the keys
         self.norm_w = t["dkv_norm"].contiguous()
 
     def kernel_units(self):
-        units = kernels.gemm_units(self.compute) + kernels.latent_attention_units(self.compute, self.rank, self.rot_dim)
+        units = kernels.gemm_units(self.compute) + kernels.latent_attention_units(self.compute, self.rank, self.rot_dim,
+                                                                                  self.dim, self.vdim)
         return units + ([("grouped_gemm", ())] if self.compute != "float32" else [])
 
     def cache_needs(self):
         return [KVNeed(1, self.rank + self.rot_dim, self.window, value_dim=0)]
 
     def weight_bytes(self):
-        per = self.uk_t.element_size()
+        per = self.uk_t.element_size()     # a decode step reads the transposed copy, not self.uk
         return self.proj.bytes() + self.o.bytes() + (self.uk_t.numel() + self.uv.numel()) * per + 4 * self.norm_w.numel()
 
     # ---- step
@@ -102,10 +104,18 @@ class LatentAttention(Part):
         qa = torch.empty((t, nh * (r + rd)), dtype=self.act_dtype, device=h.device)
         gate = torch.empty((t, nh), dtype=torch.float32, device=h.device) if self.gated else None
         rot = self.position.rotary_dim if self.position is not None else 0
+        # a prompt step whose sequences all start at position 0 (no cached prefix) may expand keys and
+        # values per head, which is less arithmetic than attention over the latent rows
+        expand = (self.window is None and t >= kernels.LATENT_EXPAND_MIN_TOKENS and ctx.host is not None
+                  and not any(ctx.host["seq_start"]) and kernels.latent_expand_usable(h.dtype, r, dim, rd, vd))
+        dense = torch.empty((t, r + rd), dtype=self.act_dtype, device=h.device) if expand else None
         kernels.latent_prepare(proj[:, :nq], proj[:, nq:nq + r + rd], proj[:, nq + r + rd:] if self.gated else None,
                                self.norm_w, self.eps, self.position.inv_freq(h.device) if rot else None, rot, self.scale,
                                q_nope, qa, gate, kc.view(-1, group.page_size, r + rd) if writes_cache else None,
-                               group.page_table, group.page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, nh, dim, rd, r)
+                               group.page_table, group.page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, nh, dim, rd, r,
+                               dense=dense)
+        if expand:
+            return self._expanded(ctx, q_nope, qa, gate, dense, residual)
         if dim:
             kernels.heads_gemm(q_nope.view(t, nh, dim), self.uk_t, qa.view(t, nh, r + rd)[:, :, :r], nh)
         else:
@@ -115,6 +125,33 @@ class LatentAttention(Part):
                                  group.page_size, self.window)
         o = torch.empty((t, nh * vd), dtype=self.act_dtype, device=h.device)
         kernels.heads_gemm(lat.view(t, nh, r), self.uv, o.view(t, nh, vd), nh, scale=gate)
+        self.o.add_into(o, residual)
+
+
+    def _expanded(self, ctx, q_nope, qa, gate, dense, residual):
+        """Attention of a prompt step over keys and values expanded per head.  Every head gets rows
+        [v | k_nope | k_rot] of its own for the step's tokens (two grouped products from the step's
+        latents, the rotated key part copied to every head) and queries [0 | q_nope | q_rot]; the
+        attention kernel then runs with vdim in the latent's place, one head per grid layer, and
+        multiplies the gate into its output."""
+        nh, dim, rd, r, vd = self.num_heads, self.dim, self.rot_dim, self.rank, self.vdim
+        t = q_nope.shape[0]
+        kd = vd + dim + rd
+        rows = torch.empty((nh, t + 64, kd), dtype=self.act_dtype, device=q_nope.device)
+        rows[:, t:].zero_()                                   # a last tile reads past the last token
+        hs = rows.stride(0)
+        kernels.grouped_gemm(dense, dense.stride(0), 0, None, 1, self.uv, vd * r, rows, kd, hs, None, None, 0, 0, None, nh, t,
+                             t, vd, r, what="latent_expand_v")
+        kernels.grouped_gemm(dense, dense.stride(0), 0, None, 1, self.uk, dim * r, rows[:, :, vd:], kd, hs, None, None, 0, 0,
+                             None, nh, t, t, dim, r, what="latent_expand_k")
+        rows[:, :t, vd + dim:] = dense[:, r:]                 # copies: the shared rotated key part, to every head
+        q = torch.empty((t, nh, kd), dtype=self.act_dtype, device=q_nope.device)
+        q[:, :, :vd].zero_()
+        q[:, :, vd:vd + dim] = q_nope.view(t, nh, dim)
+        q[:, :, vd + dim:] = qa.view(t, nh, r + rd)[:, :, r:]
+        o = torch.empty((t, nh * vd), dtype=self.act_dtype, device=q_nope.device)
+        kernels.latent_attention_mma(q.view(t, nh * kd), o, nh, vd, dim + rd, rows, None, 64, ctx.cu_seqlens, ctx.seq_start,
+                                     ctx.seq_slot, ctx.max_new, None, 1, head_stride=hs, out_scale=gate)
         self.o.add_into(o, residual)
 
 

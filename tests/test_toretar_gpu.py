@@ -11,7 +11,7 @@ import torch
 
 import plain_toretar as plain
 from replay_util import Trace, run_trace
-from tiny_configs import TORETAR_A, TORETAR_B
+from tiny_configs import TORETAR_A, TORETAR_B, TORETAR_C
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -405,6 +405,45 @@ def test_portions_long_decoding_and_reused_slots(dtype, models):
             first_round = got
         elif dtype == "float32":
             assert all(np.array_equal(got[k], first_round[k]) for k in got)
+
+
+def test_prompts_over_expanded_heads(tmp_path_factory):
+    """Prompt steps whose sequences all start at position 0 may expand keys and values per head.
+    Three unequal prompts in one step, then decoding from the cache the step left: both ways of
+    running the prompt agree with the plain implementation, and a continued prompt (a cached prefix)
+    takes the other way by itself."""
+    from gemmars_b200 import kernels
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    folder = _sharp_folder(tmp_path_factory, TORETAR_C, seed=5, factor=2.0)
+    cfg, w = plain.load_folder(folder)
+    rng = np.random.default_rng(12)
+    reqs = [rng.integers(0, cfg["vocab"], n).tolist() for n in (150, 65, 3)]
+    ref = [plain.forward(cfg, w, r + [7, 8]) for r in reqs]
+    scale = max(float(np.abs(r).max()) for r in ref)
+    was = kernels.LATENT_EXPAND_MIN_TOKENS
+    got = {}
+    try:
+        for name, threshold in (("expanded", 32), ("latent", 1 << 30)):
+            kernels.LATENT_EXPAND_MIN_TOKENS = threshold
+            before = kernels.launch_count()
+            model = build_model(folder, dtype="bfloat16")
+            runner = Runner(model, max_tokens=1024, max_batch=4)
+            slots = [runner.open() for _ in reqs]
+            out = runner.step([StepItem(s, r, range(len(r))) for s, r in zip(slots, reqs)]).cpu().numpy()
+            nxt = runner.step([StepItem(s, [7], [0]) for s in slots]).cpu().numpy()           # decoding reads the cache
+            more = runner.step([StepItem(s, [8, 9], [0]) for s in slots]).cpu().numpy()       # a continued prompt
+            got[name] = (out, nxt, more)
+            errs, at = [], 0
+            for i, r in enumerate(reqs):
+                errs += list(np.abs(out[at:at + len(r)] - ref[i][:len(r)]).max(axis=1))
+                errs.append(np.abs(nxt[i] - ref[i][len(r)]).max())
+                errs.append(np.abs(more[i] - ref[i][len(r) + 1]).max())
+                at += len(r)
+            _within(errs, TOL_BF16 * scale, "bfloat16", name)
+    finally:
+        kernels.LATENT_EXPAND_MIN_TOKENS = was
+    assert not np.array_equal(got["expanded"][0], got["latent"][0])     # the two ways are different arithmetic
+    assert np.abs(got["expanded"][0] - got["latent"][0]).max() <= 2 * TOL_BF16 * scale
 
 
 def test_greedy_generation_through_the_engine(models):

@@ -98,3 +98,13 @@ TORETAR_B = {
         _toretar_layer(9, 16, 16, 32, 128, 0.177, 1000000.0, 16, _toretar_moe(8, 2, 48, 3.0, {"ff": 64, "limit": 1.0})),
     ],
 }
+
+# Toretar whose layers all have heads much narrower than the latent: prompt steps may expand keys
+# and values per head there (vdim and dim + rot_dim multiples of 16).
+TORETAR_C = {
+    "architecture": "Toretar", "vocab": 333, "width": 128, "norm": {"eps": 1e-6},
+    "layers": [
+        _toretar_layer(4, 32, 16, 32, 128, 0.15, 10000.0, 16, _toretar_moe(4, 2, 32, 1.5, {"ff": 48, "limit": 1.2})),
+        _toretar_layer(2, 16, 16, 16, 64, 0.2, 300000.0, 8, None),
+    ],
+}
