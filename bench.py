@@ -136,18 +136,30 @@ def prefill_flops(cfg, t):
 
 
 def toretar_prefill_flops(cfg, t):
-    """Floating-point operations of a prompt of ``t`` tokens as the engine computes it (both
-    expansions on the query side: attention runs over rows of kv_rank + rot_dim)."""
+    """Floating-point operations of a prompt of ``t`` tokens from position 0, counted as useful
+    arithmetic of the way the engine takes: over expanded heads where it expands keys and values
+    (scores over dim + rot_dim, values of vdim, and the two expansions of the latents), else over
+    the latent rows (scores over kv_rank + rot_dim, values of kv_rank, and the two per-head products
+    on the query side)."""
+    import torch
+    from gemmars_b200 import kernels
     w, total = cfg["width"], 0
+    pairs = t * (t + 1) // 2
     for layer in cfg["layers"]:
         m, mlp = layer["mixer"], layer["mlp"]
         nh, dim, rd, vd, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-        per_token = 2 * (w * (nh * (dim + rd) + r + rd + nh) + nh * dim * r + nh * r * vd + nh * vd * w)
+        per_token = 2 * (w * (nh * (dim + rd) + r + rd + nh) + nh * vd * w)
+        if t >= kernels.LATENT_EXPAND_MIN_TOKENS and kernels.latent_expand_usable(torch.bfloat16, r, dim, rd, vd):
+            per_token += 2 * nh * (dim + vd) * r
+            attention = 2 * nh * (dim + rd + vd) * pairs
+        else:
+            per_token += 2 * (nh * dim * r + nh * r * vd)
+            attention = 2 * nh * (2 * r + rd) * pairs
         if mlp is not None:
             per_token += 2 * w * mlp["router"]["experts"] + 6 * w * mlp["router"]["top"] * mlp["expert"]["ff"]
             if mlp.get("shared"):
                 per_token += 6 * w * mlp["shared"]["ff"]
-        total += per_token * t + 2 * nh * (2 * r + rd) * (t * (t + 1) // 2)
+        total += per_token * t + attention
     return total + 2 * w * cfg["vocab"]
 
 

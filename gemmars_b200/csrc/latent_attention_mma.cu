@@ -19,6 +19,11 @@
 // With `ksplits` > 1 (decoding: few rows, many keys) the keys of a tile of rows are dealt to
 // ksplits CTAs, which leave (m, l, o) parts that a second kernel adds in split
 // order: the same bits every run.
+//
+// The same kernel serves a prompt step whose keys and values were expanded per head (rows
+// [v | k_nope | k_rot] with the value's width in RANK's place): head_stride > 0 gives every head rows
+// of its own, contiguous from a sequence's first packed token, one head per grid layer, and
+// out_scale (the layer's gate) is multiplied into the output.
 #include "mma.cuh"
 
 #ifndef GB_LATENT_RANK
