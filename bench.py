@@ -411,20 +411,16 @@ def kernel_table(eng, tokens, batch, context):
         toks = torch.randint(0, eng.model.plan.vocab_size, (tokens,), generator=torch.Generator().manual_seed(5)).tolist()
         for phase in ("prompt", "decode"):
             if phase == "prompt":
+                warm = runner.open()              # a warm-up prompt in a slot of its own
+                runner.step([StepItem(warm, toks, [tokens - 1])])
+                runner.close(warm)
                 slots = [runner.open()]
                 items = [StepItem(slots[0], toks, [tokens - 1])]
-                warm = [StepItem(slots[0], toks[:tokens], [])]
             else:
                 slots = [runner.open() for _ in range(batch)]
                 synthetic_fill(runner, slots, context - 2)
                 items = [StepItem(s, [1], [0]) for s in slots]
-                warm = items
-            if phase == "prompt":       # a warm-up prompt in a slot of its own
-                s2 = runner.open()
-                runner.step([StepItem(s2, toks, [tokens - 1])])
-                runner.close(s2)
-            else:
-                runner.step(warm)
+                runner.step(items)
             torch.cuda.synchronize()
             kernels.profile_start()
             runner.step(items)

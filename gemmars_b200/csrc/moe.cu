@@ -29,27 +29,9 @@ __device__ __forceinline__ void unpack(const uint4& v, float* f) {
   }
 }
 
-// Lane's share of row . xs (xs float32 in shared memory); the caller adds the lanes with warp_sum.
-// `vec`: the row starts on a 16-byte boundary and n is a multiple of the vector width.
-template <typename T>
-__device__ __forceinline__ float lane_dot(const T* __restrict__ row, const float* __restrict__ xs, int n, int lane, bool vec) {
-  float acc = 0.f;
-  if (vec) {
-    constexpr int V = Vec<T>::N;
-    const typename Vec<T>::type* r = (const typename Vec<T>::type*)row;
-    for (int i = lane; i < n / V; i += 32) {
-      float f[V];
-      unpack(r[i], f);
-#pragma unroll
-      for (int k = 0; k < V; ++k) acc = fmaf(f[k], xs[i * V + k], acc);
-    }
-  } else {
-    for (int i = lane; i < n; i += 32) acc = fmaf(to_f32(row[i]), xs[i], acc);
-  }
-  return acc;
-}
-
-// Two rows against the same xs at once: twice the loads in flight.
+// Lanes' shares of two rows . xs (xs float32 in shared memory) at once, so that twice the loads are
+// in flight; the caller adds the lanes with warp_sum.  `vec`: the rows start on 16-byte boundaries
+// and n is a multiple of the vector width.
 template <typename T>
 __device__ __forceinline__ void lane_dot2(const T* __restrict__ r0, const T* __restrict__ r1, const float* __restrict__ xs,
                                           int n, int lane, bool vec, float& a0, float& a1) {

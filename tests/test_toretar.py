@@ -104,13 +104,15 @@ def test_plain_attention_is_causal_and_gated(tmp_path):
     toks = rng.integers(0, cfg["vocab"], 12).tolist()
     full = plain.forward(cfg, w, toks)
     assert np.allclose(plain.forward(cfg, w, toks[:7]), full[:7], atol=1e-12)
-    # closing every head's gate removes the mixer: a layer without feed-forward then passes x through
+    # a layer without feed-forward adds the mixer's output and nothing else; with zero gate weights
+    # every head passes at sigmoid(0) = 1/2, so the mixer is half of what it is with the gates open
     w2 = dict(w)
     w2["l1.mix.g"] = np.zeros_like(w["l1.mix.g"])
-    w2["l1.mix.o"] = w["l1.mix.o"] * 1e3
-    res, res2 = [], []
-    plain.forward(cfg, w, toks, res)
-    plain.forward(cfg, w2, toks, res2)
-    h = plain.rms_norm(res2[0], w2["l1.norm1"], cfg["norm"]["eps"])
-    half = plain.latent_attention(h, w2, "l1.mix.", cfg["layers"][1]["mixer"], cfg["norm"]["eps"])
-    assert np.allclose(res2[1], res2[0] + half, atol=1e-9) and np.abs(half).max() > 0   # sigmoid(0) = 1/2, not closed
+    res = []
+    plain.forward(cfg, w2, toks, res)
+    h = plain.rms_norm(res[0], w2["l1.norm1"], cfg["norm"]["eps"])
+    halved = plain.latent_attention(h, w2, "l1.mix.", cfg["layers"][1]["mixer"], cfg["norm"]["eps"])
+    assert np.allclose(res[1], res[0] + halved, atol=1e-9) and np.abs(halved).max() > 0
+    w3 = dict(w2)
+    w3["l1.mix.o"] = 2.0 * w2["l1.mix.o"]
+    assert np.allclose(plain.latent_attention(h, w3, "l1.mix.", cfg["layers"][1]["mixer"], cfg["norm"]["eps"]), 2.0 * halved)
