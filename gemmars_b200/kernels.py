@@ -612,6 +612,19 @@ def gemm_swiglu(x, w_gate_up, out):
     silu_mul(gu, out)
 
 
+def gemm_gated(x, w_gate_up, out, act: str = "silu"):
+    """out = act(x @ gate.T) * (x @ up.T) for the stacked [gate; up]: the fused kernel for SiLU,
+    the product followed by ``gated_act`` for the other activations."""
+    if act == "silu":
+        gemm_swiglu(x, w_gate_up, out)
+        return
+    if isinstance(x, UnscaledRows):
+        x = x.materialize()
+    gu = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=x.dtype, device=x.device)
+    gemm(x, w_gate_up, gu)
+    gated_act(gu, out, act)
+
+
 _STATUS_ENTRIES = ("gb_gemm_tc_status", "gb_attention_prefill_tc_status", "gb_attention_decode_stream_status")
 
 
@@ -1315,3 +1328,206 @@ def attention(ctx, q, out, nh, kcache, vcache, page_table, page_size, window=Non
 
 # a step whose sequences bring at most this many tokens each runs the per-position decode kernel
 DECODE_KERNEL_MAX_NEW = 1
+
+
+# --------------------------------------------------------------------------- rows: second tables, norms after a sublayer
+
+ACT_SILU, ACT_GELU_TANH = 0, 1
+GATED_ACTS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
+
+
+def gather_add(table: torch.Tensor, idx: torch.Tensor, x: torch.Tensor):
+    """x[t] += table[idx[t]]; x is the float32 residual stream [T, H]."""
+    _cuda(table, idx, x)
+    assert idx.dtype == torch.int32 and x.dtype == torch.float32 and x.is_contiguous() and table.is_contiguous()
+    assert table.shape[1] == x.shape[1] and idx.numel() == x.shape[0]
+    f = _fn("rows", "gb_gather_add", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(table.data_ptr(), dtype_code(table.dtype), idx.data_ptr(), x.data_ptr(), idx.numel(), table.shape[1],
+             table.shape[0], _stream()), "gather_add", "embed",
+           2 * _nbytes(x) + idx.numel() * table.shape[1] * table.element_size())
+
+
+def rmsnorm_add(y: torch.Tensor, weight: torch.Tensor, x: torch.Tensor, eps: float):
+    """x[t] += y[t] * (mean(y[t]^2) + eps)^-1/2 * weight: a norm on a sublayer's output, added into
+    the float32 residual stream."""
+    _cuda(y, weight, x)
+    assert y.dtype == torch.float32 and x.dtype == torch.float32 and weight.dtype == torch.float32
+    assert y.is_contiguous() and x.is_contiguous() and y.shape == x.shape and weight.numel() == x.shape[-1]
+    n = x.shape[-1]
+    f = _fn("rows", "gb_rmsnorm_add", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p])
+    _check(f(y.data_ptr(), weight.data_ptr(), x.data_ptr(), x.numel() // n, n, eps, _stream()), "rmsnorm_add", "norm",
+           _nbytes(y, weight) + 2 * _nbytes(x))
+
+
+def gated_act(gu: torch.Tensor, out: torch.Tensor, act: str = "silu"):
+    """out[t, i] = act(gu[t, i]) * gu[t, I + i], act one of GATED_ACTS."""
+    _cuda(gu, out)
+    inter = out.shape[-1]
+    assert gu.shape[-1] == 2 * inter and gu.dtype == out.dtype and gu.is_contiguous() and out.is_contiguous()
+    f = _fn("rows", "gb_gated_act", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(gu.data_ptr(), out.data_ptr(), dtype_code(out.dtype), out.numel() // inter, inter, GATED_ACTS[act],
+             _stream()), "gated_act", "elementwise", _nbytes(gu, out))
+
+
+def scale_rows(y: torch.Tensor, s: float):
+    """y *= s in place (float32)."""
+    _cuda(y)
+    assert y.dtype == torch.float32 and y.is_contiguous()
+    f = _fn("rows", "gb_scale_f32", [c_void_p, c_longlong, c_float, c_void_p])
+    _check(f(y.data_ptr(), y.numel(), s, _stream()), "scale_rows", "elementwise", 2 * _nbytes(y))
+
+
+# --------------------------------------------------------------------------- mixers with a state per sequence
+
+def _cols(t: torch.Tensor):
+    """A [T, n] tensor or a slice of columns of one: unit stride inside a row."""
+    assert t.dim() == 2 and t.stride(1) == 1
+    return t.data_ptr(), t.stride(0)
+
+
+def short_filter(u, taps, bias, state, cu_seqlens, tok_seq, seq_slot, out, act: bool = False, update_state: bool = True):
+    """out[t, c] = act(bias[c] + sum_j taps[c, j] u[t - K + 1 + j, c]) along each sequence of the
+    packed step; the rows before the step's first come from ``state`` [slots + 1, K - 1, C]
+    (float32, oldest first), which then takes the sequence's last K - 1 inputs.  ``u`` and ``out``
+    may be slices of columns; ``act``: SiLU."""
+    _cuda(u, taps, bias, state, cu_seqlens, tok_seq, seq_slot, out)
+    c, k = taps.shape
+    assert taps.dtype == torch.float32 and taps.is_contiguous() and u.shape[1] == c and out.shape == u.shape
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (max(k - 1, 0), c)
+    up, ldu = _cols(u)
+    op, ldo = _cols(out)
+    f = _fn("recurrent", "gb_short_filter",
+            [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+             c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(up, dtype_code(u.dtype), ldu, taps.data_ptr(), _ptr(bias), state.data_ptr(), cu_seqlens.data_ptr(),
+             tok_seq.data_ptr(), seq_slot.data_ptr(), op, dtype_code(out.dtype), ldo, u.shape[0], seq_slot.numel(), c, k,
+             1 if act else 0, 1 if update_state else 0, _stream()), "short_filter", "elementwise",
+           u.numel() * u.element_size() + out.numel() * out.element_size())
+    if update_state and k > 1:
+        count_launches(1)
+
+
+def short_filter_state(u, state, cu_seqlens, seq_slot, k: int):
+    """Only the state's update of ``short_filter``."""
+    _cuda(u, state, cu_seqlens, seq_slot)
+    if k <= 1:
+        return
+    c = u.shape[1]
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (k - 1, c)
+    up, ldu = _cols(u)
+    f = _fn("recurrent", "gb_short_filter_state",
+            [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(up, dtype_code(u.dtype), ldu, state.data_ptr(), cu_seqlens.data_ptr(), seq_slot.data_ptr(), seq_slot.numel(),
+             c, k, _stream()), "short_filter_state", "elementwise", 0)
+
+
+def delta_rule(q, k, v, beta_logit, a_logit, a_log, dt_bias, state, cu_seqlens, seq_slot, y, heads, groups, dim, vdim,
+               q_scale):
+    """The gated delta rule over each sequence of the packed step (float32 throughout):
+    S <- g S; u = beta (v - S^T k^); S <- S + k^ u^T; y = S^T q^, with k^, q^ the unit vectors of k
+    and q (q^ times ``q_scale``), beta = sigmoid(beta_logit), g = exp(-exp(a_log) softplus(a_logit +
+    dt_bias)).  q, k, v: slices of columns of one [T, *] tensor; ``state`` [slots + 1, heads, dim, vdim]."""
+    _cuda(q, k, v, beta_logit, a_logit, a_log, dt_bias, state, cu_seqlens, seq_slot, y)
+    for t in (q, k, v, beta_logit, a_logit, y, state):
+        assert t.dtype == torch.float32
+    qp, ld = _cols(q)
+    kp, ldk = _cols(k)
+    vp, ldv = _cols(v)
+    bp, ldg = _cols(beta_logit)
+    ap, lda = _cols(a_logit)
+    assert ld == ldk == ldv and ldg == lda and y.is_contiguous() and y.shape[1] == heads * vdim
+    assert state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim)
+    f = _fn("recurrent", "gb_delta_rule",
+            [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(qp, kp, vp, ld, bp, ap, ldg, a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(), cu_seqlens.data_ptr(),
+             seq_slot.data_ptr(), y.data_ptr(), seq_slot.numel(), heads, groups, dim, vdim, q_scale, _stream()),
+           "delta_rule", "attention", _nbytes(y) * 2 + 2 * seq_slot.numel() * heads * dim * vdim * 4)
+
+
+def ssd_scan(x, b, c, dt_raw, a_log, dt_bias, skip, state, cu_seqlens, seq_slot, y, heads, groups, n_state, vdim):
+    """The state-space recurrence with one decay per head over each sequence of the packed step
+    (float32): dt = softplus(dt_raw + dt_bias); S <- exp(-exp(a_log) dt) S + dt B x^T; y = S^T C +
+    skip x.  x, b, c: slices of columns of one tensor; ``state`` [slots + 1, heads, n_state, vdim]."""
+    _cuda(x, b, c, dt_raw, a_log, dt_bias, skip, state, cu_seqlens, seq_slot, y)
+    for t in (x, b, c, dt_raw, y, state):
+        assert t.dtype == torch.float32
+    xp, ld = _cols(x)
+    bp, ldb = _cols(b)
+    cp, ldc = _cols(c)
+    dp, ldd = _cols(dt_raw)
+    assert ld == ldb == ldc and y.is_contiguous() and y.shape[1] == heads * vdim
+    assert state.is_contiguous() and tuple(state.shape[1:]) == (heads, n_state, vdim)
+    f = _fn("recurrent", "gb_ssd_scan",
+            [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(xp, bp, cp, ld, dp, ldd, a_log.data_ptr(), dt_bias.data_ptr(), skip.data_ptr(), state.data_ptr(),
+             cu_seqlens.data_ptr(), seq_slot.data_ptr(), y.data_ptr(), seq_slot.numel(), heads, groups, n_state, vdim,
+             _stream()), "ssd_scan", "attention", _nbytes(y) * 2 + 2 * seq_slot.numel() * heads * n_state * vdim * 4)
+
+
+def gated_group_norm(y, gate, weight, out, group_size: int, eps: float, gate_first: bool, out_scale: float = 1.0):
+    """Rows of float32 ``y`` [T, n] in groups of ``group_size`` channels, each group divided by its
+    root mean square, channel i times weight[i % len(weight)] and silu(gate[t, i]); with
+    ``gate_first`` the gate goes in before the statistics.  ``gate``: float32, may be a slice."""
+    _cuda(y, gate, weight, out)
+    assert y.dtype == torch.float32 and gate.dtype == torch.float32 and weight.dtype == torch.float32
+    assert y.is_contiguous() and out.is_contiguous() and out.shape == y.shape and gate.shape == y.shape
+    gp, ldg = _cols(gate)
+    f = _fn("recurrent", "gb_gated_group_norm",
+            [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_float,
+             c_void_p])
+    _check(f(y.data_ptr(), gp, ldg, weight.data_ptr(), weight.numel(), out.data_ptr(), dtype_code(out.dtype), y.shape[0],
+             y.shape[1], group_size, eps, 1 if gate_first else 0, out_scale, _stream()), "gated_group_norm", "norm",
+           _nbytes(y, out) + y.numel() * 4)
+
+
+# --------------------------------------------------------------------------- attention with capped scores
+
+def filter_rope_cache(u, taps, state, inv_freq, rot, ctx_pos, tok_seq, seq_slot, cu_seqlens, page_table, page_size, q_out,
+                      kcache, vcache, heads, groups, dim, vdim):
+    """The columns [q | k | v] of ``u`` through a short causal filter (``taps`` [channels, K] or
+    None), the first ``rot`` dims of each q and k head rotated (pairs i, i + rot/2), then q into
+    ``q_out`` [T, heads * dim] and keys and values into their pages (None: not kept)."""
+    _cuda(u, taps, state, inv_freq, ctx_pos, tok_seq, seq_slot, cu_seqlens, page_table, q_out, kcache, vcache)
+    channels = (heads + groups) * dim + groups * vdim
+    k = 0 if taps is None else taps.shape[1]
+    up, ldu = _cols(u)
+    qp, ldq = _cols(q_out)
+    assert u.shape[1] == channels and q_out.dtype == u.dtype
+    if taps is not None:
+        assert taps.dtype == torch.float32 and taps.is_contiguous() and taps.shape[0] == channels
+    if k > 1:
+        assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (k - 1, channels)
+    if kcache is not None:
+        assert kcache.dtype == u.dtype and vcache.dtype == u.dtype and kcache.is_contiguous() and vcache.is_contiguous()
+        assert tuple(kcache.shape[1:]) == (groups, page_size, dim) and tuple(vcache.shape[1:]) == (groups, vdim, page_size)
+    f = _fn("attention_capped", "gb_filter_rope_cache",
+            [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(up, dtype_code(u.dtype), ldu, _ptr(taps), _ptr(state) if k > 1 else None, k, _ptr(inv_freq) if rot else None,
+             rot, ctx_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), cu_seqlens.data_ptr(), _ptr(page_table),
+             page_table.shape[1] if page_table is not None else 1, page_size, qp, ldq, _ptr(kcache), _ptr(vcache),
+             u.shape[0], heads, groups, dim, vdim, _stream()), "filter_rope_cache", "elementwise",
+           2 * u.numel() * u.element_size())
+
+
+def attention_capped(ctx, q, out, heads, kcache, vcache, page_table, page_size, window, scale, cap, gate=None,
+                     out_scale: float = 1.0):
+    """Attention of the step's queries [T, heads * dim] over the cache with keys of ``dim`` and
+    values of ``vdim``: score = (q . k) * scale, capped as cap * tanh(score / cap) when ``cap``;
+    a window of ``window`` keys when given; the output times sigmoid(gate) * out_scale."""
+    _cuda(q, out, kcache, vcache, page_table, gate)
+    groups, dim, vdim = kcache.shape[1], kcache.shape[3], vcache.shape[2]
+    qp, ldq = _cols(q)
+    op, ldo = _cols(out)
+    gp, ldg = _cols(gate) if gate is not None else (None, 0)
+    assert q.dtype == out.dtype == kcache.dtype == vcache.dtype and (gate is None or gate.dtype == q.dtype)
+    assert q.shape[1] == heads * dim and out.shape[1] == heads * vdim
+    f = _fn("attention_capped", "gb_attention_capped",
+            [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_longlong, c_float, c_void_p])
+    _check(f(qp, ldq, op, ldo, dtype_code(q.dtype), kcache.data_ptr(), vcache.data_ptr(), page_table.data_ptr(),
+             page_table.shape[1], page_size, groups, dim, vdim, ctx.tok_pos.data_ptr(), ctx.tok_seq.data_ptr(),
+             ctx.seq_slot.data_ptr(), q.shape[0], heads, int(window or 0), scale, float(cap or 0.0), gp, ldg, out_scale,
+             _stream()), "attention_capped", "attention", 2 * q.numel() * q.element_size())

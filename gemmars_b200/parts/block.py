@@ -1,10 +1,13 @@
 """The arrangement of a layer's parts.
 
 ``prenorm`` (src/qwen.rs:682-696): x += mixer(norm(x)); x += ffn(norm(x)), the residual stream
-``x`` in float32.  ``parallel``: x += mixer(norm(x)) + ffn(norm(x)) with one norm.  Another
-arrangement (post-norm, a third norm) is another class like these, registered under its own kind
+``x`` in float32.  ``parallel``: x += mixer(norm(x)) + ffn(norm(x)) with one norm.  ``sandwich``:
+a norm on both sides of each sublayer, x += post(mixer(pre(x))); x += post(ffn(pre(x))).  Another
+arrangement (a third norm) is another class like these, registered under its own kind
 and reading its own part names from the layer's spec."""
 from __future__ import annotations
+
+import torch
 
 from .. import kernels
 from .base import Block, register_part
@@ -75,9 +78,43 @@ class ParallelBlock(Block):
             self.ffn.forward(ctx, h, x)
 
 
+class SandwichBlock(Block):
+    """``sandwich``: x += mixer_post_norm(mixer(mixer_norm(x))); x += ffn_post_norm(ffn(ffn_norm(x))).
+    A sublayer adds its output into float32 rows of zeros instead of the residual stream; the norm
+    after it reads those rows and adds the normed rows into the stream.  The layer's spec lists
+    ``mixer_norm``, ``mixer``, ``mixer_post_norm`` and, when the layer has a feed-forward,
+    ``ffn_norm``, ``ffn``, ``ffn_post_norm``."""
+
+    def __init__(self, layer_spec, compute):
+        super().__init__(layer_spec, compute)
+        self.mixer_norm = self.need("mixer_norm", "norm")
+        self.mixer = self.need("mixer", "mixer")
+        self.mixer_post_norm = self.need("mixer_post_norm", "norm")
+        self.ffn = self.need("ffn", "ffn") if "ffn" in layer_spec.parts else None
+        self.ffn_norm = self.need("ffn_norm", "norm") if self.ffn is not None else None
+        self.ffn_post_norm = self.need("ffn_post_norm", "norm") if self.ffn is not None else None
+
+    def parts(self):
+        out = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "mixer_post_norm": self.mixer_post_norm}
+        if self.ffn is not None:
+            out.update({"ffn_norm": self.ffn_norm, "ffn": self.ffn, "ffn_post_norm": self.ffn_post_norm})
+        return out
+
+    def forward(self, ctx, x, caches, writes_cache=True):
+        mine = self.split_caches(caches)
+        y = torch.zeros_like(x)
+        self.mixer.forward(ctx, self.mixer_norm.forward(ctx, x), y, mine["mixer"], writes_cache)
+        self.mixer_post_norm.add_normed(ctx, y, x)
+        if self.ffn is not None:
+            y.zero_()
+            self.ffn.forward(ctx, self.ffn_norm.forward(ctx, x), y)
+            self.ffn_post_norm.add_normed(ctx, y, x)
+
+
 def _plain(h):
     return h.materialize() if isinstance(h, kernels.UnscaledRows) else h
 
 
 register_part("block", "prenorm", PreNormBlock)
 register_part("block", "parallel", ParallelBlock)
+register_part("block", "sandwich", SandwichBlock)

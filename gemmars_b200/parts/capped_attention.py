@@ -1,0 +1,117 @@
+"""Softmax attention beside ``Attention`` for designs whose scores are capped, whose values are
+wider or narrower than their keys, or whose q, k and v pass a short filter over time.
+
+For one token, with h the mixer's input:
+  q, k, v = W_q h, W_k h, W_v h (+ biases), heads x dim, kv_heads x dim, kv_heads x vdim;
+  each channel passes a causal filter over time (``conv`` taps, no bias, no activation; 0: none);
+  the position encoding turns q and k (a ``rotary`` part with the "half" layout, or None);
+  score = (q . k) * scale, then cap * tanh(score / cap) when ``softcap``; a query sees itself and
+  the ``window`` - 1 positions before it (None: all); ordinary softmax; the heads side by side are
+  multiplied by sigmoid(W_g h) when ``gate``, then W_o, added into the residual.
+
+Keys (filtered and rotated) and values (filtered) live in the paged cache that every attention
+of the package uses (a window's pages are a ring); the filter's last ``conv`` - 1 inputs are a
+state per sequence.  Scores, softmax, angles and the gate are float32.  Parameters: hidden_size,
+heads, kv_heads, dim, vdim, bias, conv, window, scale, softcap, gate, position, out_scale.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..cache.pool import KVNeed, StateNeed
+from .base import Part, TensorWant, build_part, register_part
+from .linear import Linear
+from .rotary import Rotary
+
+
+class CappedAttention(Part):
+    category = "mixer"
+
+    def __init__(self, spec, compute):
+        super().__init__(spec, compute)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.heads, self.kv_heads = int(p["heads"]), int(p["kv_heads"])
+        self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
+        self.bias, self.gate = bool(p.get("bias", False)), bool(p.get("gate", False))
+        self.taps = int(p.get("conv") or 0)
+        self.window = p.get("window")
+        self.scale = float(p["scale"]) if p.get("scale") is not None else float(self.dim) ** -0.5
+        self.softcap = float(p.get("softcap") or 0.0)
+        self.out_scale = float(p.get("out_scale", 1.0))
+        if self.heads % self.kv_heads:
+            raise ValueError(f"capped_attention: {self.heads} heads are not a multiple of {self.kv_heads} kv heads")
+        if self.vdim > 256:
+            raise ValueError(f"capped_attention: values of {self.vdim} are wider than the kernel takes (256)")
+        if not 0 <= self.taps <= 8:
+            raise ValueError(f"capped_attention: a filter of {self.taps} taps is not supported (0 to 8)")
+        pos = p.get("position")
+        self.position = build_part("position", pos, compute) if pos is not None else None
+        if self.position is not None and not (isinstance(self.position, Rotary) and self.position.layout == "half"):
+            raise ValueError("capped_attention: the position encoding must be a rotary part with the half layout")
+        self.channels = (self.heads + self.kv_heads) * self.dim + self.kv_heads * self.vdim     # q | k | v
+        self.proj = self.o = self.filter = None
+
+    def wants(self):
+        h, nh, nkv, d, vd = self.hidden_size, self.heads, self.kv_heads, self.dim, self.vdim
+        w = {"q": TensorWant((nh * d, h)), "k": TensorWant((nkv * d, h)), "v": TensorWant((nkv * vd, h)),
+             "o": TensorWant((h, nh * vd))}
+        if self.bias:
+            w.update({"q_bias": TensorWant((nh * d,), "vector"), "k_bias": TensorWant((nkv * d,), "vector"),
+                      "v_bias": TensorWant((nkv * vd,), "vector")})
+        if self.taps:
+            w.update({"q_conv": TensorWant((nh * d, self.taps), "vector"), "k_conv": TensorWant((nkv * d, self.taps), "vector"),
+                      "v_conv": TensorWant((nkv * vd, self.taps), "vector")})
+        if self.gate:
+            w["g"] = TensorWant((nh * vd, h))
+        return w
+
+    def load(self, t):
+        names = ["q", "k", "v"] + (["g"] if self.gate else [])
+        bias = None
+        if self.bias:
+            parts = [t["q_bias"], t["k_bias"], t["v_bias"]]
+            if self.gate:
+                parts.append(torch.zeros(self.heads * self.vdim, dtype=torch.float32, device=t["q_bias"].device))
+            bias = torch.cat(parts)
+        self.proj = Linear(torch.cat([t[n] for n in names], dim=0), bias)     # one product: [q | k | v | gate]
+        self.o = Linear(t["o"])
+        if self.taps:
+            self.filter = torch.cat([t["q_conv"], t["k_conv"], t["v_conv"]], dim=0).contiguous()
+
+    def kernel_units(self):
+        return (kernels.gemm_units(self.compute) + [("attention_capped", ())]
+                + ([("recurrent", ())] if self.taps > 1 else []))
+
+    def cache_needs(self):
+        needs = [KVNeed(self.kv_heads, self.dim, self.window, self.vdim)]
+        if self.taps > 1:
+            needs.append(StateNeed((self.taps - 1, self.channels)))
+        return needs
+
+    def weight_bytes(self):
+        return self.proj.bytes() + self.o.bytes() + (4 * self.filter.numel() if self.filter is not None else 0)
+
+    def forward(self, ctx, h, residual, caches, writes_cache=True):
+        if not writes_cache:
+            raise ValueError("capped_attention: running on another layer's keys and values is not supported")
+        group, kc, vc = caches[0]
+        filter_state = caches[1] if self.taps > 1 else None
+        nh, d, vd, c = self.heads, self.dim, self.vdim, self.channels
+        p = self.proj(h)
+        t = p.shape[0]
+        rot = self.position.rotary_dim if self.position is not None else 0
+        q = torch.empty((t, nh * d), dtype=p.dtype, device=p.device)
+        kernels.filter_rope_cache(p[:, :c], self.filter, filter_state, self.position.inv_freq(p.device) if rot else None, rot,
+                                  ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, ctx.cu_seqlens, group.page_table, group.page_size,
+                                  q, kc, vc, nh, self.kv_heads, d, vd)
+        if self.taps > 1:
+            kernels.short_filter_state(p[:, :c], filter_state, ctx.cu_seqlens, ctx.seq_slot, self.taps)
+        att = torch.empty((t, nh * vd), dtype=p.dtype, device=p.device)
+        kernels.attention_capped(ctx, q, att, nh, kc, vc, group.page_table, group.page_size, self.window, self.scale,
+                                 self.softcap, p[:, c:] if self.gate else None, self.out_scale)
+        self.o.add_into(att, residual)
+
+
+register_part("mixer", "capped_attention", CappedAttention)

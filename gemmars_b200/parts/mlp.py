@@ -1,5 +1,6 @@
 """Gated feed-forward: down(act(gate(x)) * up(x)), act = SiLU (src/qwen.rs:57-68,
-silu(a) = a / (1 + exp(-a)) src/kernels.rs:1416-1426).  The gate and up matrices are stacked at
+silu(a) = a / (1 + exp(-a)) src/kernels.rs:1416-1426) or, with ``activation: gelu_tanh``,
+0.5 a (1 + tanh(sqrt(2/pi) (a + 0.044715 a^3))).  The gate and up matrices are stacked at
 load into one [2I, H] matrix so one product reads the input once."""
 from __future__ import annotations
 
@@ -17,9 +18,9 @@ class GatedMLP(Part):
         super().__init__(spec, compute)
         self.hidden_size = int(spec.params["hidden_size"])
         self.intermediate_size = int(spec.params["intermediate_size"])
-        act = spec.params.get("activation", "silu")
-        if act != "silu":
-            raise ValueError(f"gated_mlp: activation {act!r} has no kernel (known: silu)")
+        self.activation = act = spec.params.get("activation", "silu")
+        if act not in kernels.GATED_ACTS:
+            raise ValueError(f"gated_mlp: activation {act!r} has no kernel (known: {', '.join(kernels.GATED_ACTS)})")
         self.gate_up = self.down = None
 
     def wants(self):
@@ -31,7 +32,7 @@ class GatedMLP(Part):
         self.down = Linear(tensors["down"])
 
     def kernel_units(self):
-        return kernels.gemm_units(self.compute) + [("elementwise", ())]
+        return kernels.gemm_units(self.compute) + [("elementwise", ()), ("rows", ())]
 
     #: forward takes ``then_norm`` and may be given kernels.UnscaledRows for ``h``
     links_norms = True
@@ -41,7 +42,7 @@ class GatedMLP(Part):
         reads the residual next; returns that norm's input where the down product could leave it."""
         rows = h.rows if isinstance(h, kernels.UnscaledRows) else h
         a = torch.empty((rows.shape[0], self.intermediate_size), dtype=rows.dtype, device=rows.device)
-        kernels.gemm_swiglu(h, self.gate_up.weight, a)
+        kernels.gemm_gated(h, self.gate_up.weight, a, self.activation)
         return self.down.add_into(a, residual, then_norm)
 
     def weight_bytes(self):

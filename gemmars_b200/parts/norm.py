@@ -1,6 +1,11 @@
 """RMSNorm: out = x * (mean(x^2) + eps)^-1/2 * w, statistics in float32
 (src/kernels.rs:1385-1392; the weight is used as stored, not as 1 + w: src/qwen.rs:343-346 with
-src/config.rs:465-469).  Input: rows of the float32 residual stream; output: activations."""
+src/config.rs:465-469).  Input: rows of the float32 residual stream; output: activations.
+
+``offset`` (default 0): the stored weight is a deviation from it, w = offset + stored (a
+checkpoint that keeps its norm weights around zero has offset 1); the sum is taken once, in
+float32, when the weight is loaded.  ``add_normed`` is the norm on the other side of a sublayer:
+it norms the sublayer's float32 output and adds it into the residual stream."""
 from __future__ import annotations
 
 import torch
@@ -19,16 +24,19 @@ class RMSNorm(Part):
         super().__init__(spec, compute)
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
+        self.offset = float(spec.params.get("offset", 0.0))
         self.weight = None
 
     def wants(self):
         return {"weight": TensorWant((self.size,), "vector")}
 
     def load(self, tensors):
-        self.weight = tensors["weight"].contiguous()
+        w = tensors["weight"].to(torch.float32)
+        self.weight = (w + self.offset if self.offset else w).contiguous()
 
     def kernel_units(self):
-        return [("elementwise", ())]
+        # the unit of ``add_normed`` is built ahead only for a norm whose plan says it sits after a sublayer
+        return [("rows", ())] if self.spec.params.get("after_sublayer") else [("elementwise", ())]
 
     def weight_bytes(self):
         return 0 if self.weight is None else 4 * self.weight.numel()
@@ -38,6 +46,10 @@ class RMSNorm(Part):
         out = torch.empty((rows, self.size), dtype=self.act_dtype, device=x.device)
         kernels.rmsnorm(x, self.weight, out, self.eps, rows_index)
         return out
+
+    def add_normed(self, ctx, y, x):
+        """x += norm(y): ``y`` a sublayer's float32 output, ``x`` the residual stream."""
+        kernels.rmsnorm_add(y, self.weight, x, self.eps)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -3,7 +3,7 @@
 
 Every tensor has a generator of its own, seeded from the seed and the tensor's name, so a
 tensor's values do not depend on which other tensors exist.  Matrices, the embedding and biases
-are N(0, 0.02); norm weights are 1 + N(0, 0.1).  Values are drawn in float32 and stored in
+are N(0, 0.02); norm weights are 1 + N(0, 0.1); the other kinds are listed at ``_STD``.  Values are drawn in float32 and stored in
 bfloat16 (or kept in float32 when asked, which gives weights that bfloat16 cannot hold).
 
 Reference: the reference has no random-weights mode for models (only LCG data in its kernel
@@ -20,7 +20,10 @@ import torch
 from ..config.registry import resolve_architecture
 from .safetensors_io import write_safetensors
 
-_STD = {"matrix": (0.0, 0.02), "bias": (0.0, 0.02), "norm": (1.0, 0.1)}
+_STD = {"matrix": (0.0, 0.02), "bias": (0.0, 0.02), "norm": (1.0, 0.1),
+        # weights kept around zero (a norm stored as a deviation from one, a step-size bias), the taps
+        # of a short filter over time, and the logarithm of a decay rate
+        "small": (0.0, 0.1), "filter": (0.0, 0.4), "log_rate": (0.0, 0.5)}
 
 
 def _fnv1a(text: str) -> int:
