@@ -16,6 +16,7 @@
 
 constexpr int CHUNK = 128;
 constexpr int MAX_TAPS = 8;
+constexpr int VPT = 4;   // value dims a thread keeps: values up to VPT * CHUNK wide
 
 template <typename T>
 __device__ __forceinline__ float filtered(const T* __restrict__ u, long long ldu, int row0, int local,
@@ -125,7 +126,7 @@ __global__ void __launch_bounds__(CHUNK) attention_capped_kernel(
   for (int i = tid; i < D; i += CHUNK) qs[i] = to_f32(qrow[i]);
   __syncthreads();
   const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
-  float m = -INFINITY, l = 0.f, acc[2] = {0.f, 0.f};
+  float m = -INFINITY, l = 0.f, acc[VPT] = {};
   for (int c0 = lo; c0 < hi; c0 += CHUNK) {
     const int j = c0 + tid;
     float s = -INFINITY;
@@ -147,7 +148,7 @@ __global__ void __launch_bounds__(CHUNK) attention_capped_kernel(
     l = l * alpha + csum;
     const int n = min(CHUNK, hi - c0);
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
+    for (int u = 0; u < VPT; ++u) {
       const int d = tid + u * CHUNK;
       if (d < Vd) {
         float a = acc[u] * alpha;
@@ -160,7 +161,7 @@ __global__ void __launch_bounds__(CHUNK) attention_capped_kernel(
   }
   T* orow = out + (size_t)t * out_stride + (size_t)h * Vd;
 #pragma unroll
-  for (int u = 0; u < 2; ++u) {
+  for (int u = 0; u < VPT; ++u) {
     const int d = tid + u * CHUNK;
     if (d < Vd) {
       float o = acc[u] / l;
@@ -176,7 +177,7 @@ GB_EXPORT int gb_attention_capped(const void* q, long long q_stride, void* out, 
                                   int H, int window, float scale, float cap, const void* gate, long long gate_stride,
                                   float out_scale, cudaStream_t stream) {
   if (ntok <= 0) return 0;
-  if (D <= 0 || Vd <= 0 || Vd > 2 * CHUNK || G <= 0 || H % G) return GB_ERR_SIZE;
+  if (D <= 0 || Vd <= 0 || Vd > VPT * CHUNK || G <= 0 || H % G) return GB_ERR_SIZE;
   const size_t smem = (size_t)(D + CHUNK + 34) * sizeof(float) + CHUNK * sizeof(size_t) + 8;
   dim3 grid(ntok, H);
   if (dtype == GB_F32)

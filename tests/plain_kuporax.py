@@ -66,6 +66,58 @@ def rotate_half(x, positions, base, dims):
     return out
 
 
+# ---- recurrences and attention on prepared inputs
+def delta_scan(q, k, v, beta, decay, state=None):
+    """q, k [T, G, D] (unit vectors, q scaled), v [T, H, V], beta and decay [T, H].  Per head:
+    S <- decay S; u = beta (v - S^T k); S <- S + k u^T; out = S^T q.  Returns (out [T, H, V], S [H, D, V])."""
+    T, H, V = v.shape
+    G, D = q.shape[1], q.shape[2]
+    S = np.zeros((H, D, V)) if state is None else state.copy()
+    out = np.zeros((T, H, V))
+    for head in range(H):
+        g = head // (H // G)
+        for t in range(T):
+            S[head] = decay[t, head] * S[head]
+            u = beta[t, head] * (v[t, head] - S[head].T @ k[t, g])
+            S[head] = S[head] + np.outer(k[t, g], u)
+            out[t, head] = S[head].T @ q[t, g]
+    return out, S
+
+
+def ssd_scan(x, B, C, dt, rate, skip, state=None):
+    """x [T, H, V], B and C [T, G, N], dt [T, H] (after softplus), rate = exp(A_log) [H], skip [H].
+    S <- exp(-rate dt) S + dt B x^T; y = S^T C + skip x.  Returns (y [T, H, V], S [H, N, V])."""
+    T, H, V = x.shape
+    G, N = B.shape[1], B.shape[2]
+    S = np.zeros((H, N, V)) if state is None else state.copy()
+    y = np.zeros((T, H, V))
+    for head in range(H):
+        g = head // (H // G)
+        for t in range(T):
+            S[head] = np.exp(-rate[head] * dt[t, head]) * S[head] + dt[t, head] * np.outer(B[t, g], x[t, head])
+            y[t, head] = S[head].T @ C[t, g] + skip[head] * x[t, head]
+    return y, S
+
+
+def capped_attention(q, k, v, q_pos, k_pos, scale, cap, size):
+    """q [Tq, H, D] at positions q_pos, k [Tk, G, D] and v [Tk, G, V] at positions k_pos.  A query
+    at i sees the keys at j with 0 <= i - j < size (all earlier ones when size is None).
+    score = (q . k) scale, then cap tanh(score / cap) when cap; softmax.  Returns [Tq, H, V]."""
+    H, G = q.shape[1], k.shape[1]
+    dist = np.asarray(q_pos)[:, None] - np.asarray(k_pos)[None, :]
+    seen = (dist >= 0) & ((dist < size) if size else True)
+    out = np.zeros((q.shape[0], H, v.shape[2]))
+    for head in range(H):
+        g = head // (H // G)
+        s = (q[:, head] @ k[:, g].T) * scale
+        if cap:
+            s = cap * np.tanh(s / cap)
+        s = np.where(seen, s, -np.inf)
+        p = np.exp(s - s.max(-1, keepdims=True))
+        out[:, head] = (p / p.sum(-1, keepdims=True)) @ v[:, g]
+    return out
+
+
 # ---- mixers
 def delta_mixer(h, P, m, eps):
     """Gated delta rule.  P: the mixer's tensors by short name; m: its sizes."""
@@ -79,15 +131,7 @@ def delta_mixer(h, P, m, eps):
     beta = sigmoid(h @ P["b"].T)                                            # [T, H]
     decay = np.exp(-np.exp(P["A_log"]) * softplus(h @ P["a"].T + P["dt_bias"]))
     gate = silu(h @ P["g"].T).reshape(T, H, V)
-    out = np.zeros((T, H, V))
-    for head in range(H):
-        g = head // (H // G)
-        S = np.zeros((D, V))
-        for t in range(T):
-            S = decay[t, head] * S
-            u = beta[t, head] * (v[t, head] - S.T @ k[t, g])
-            S = S + np.outer(k[t, g], u)
-            out[t, head] = S.T @ q[t, g]
+    out, _ = delta_scan(q, k, v, beta, decay)
     out = rms_scale(out, eps) * P["norm"] * gate
     return out.reshape(T, H * V) @ P["o"].T
 
@@ -98,23 +142,12 @@ def window_attention(h, P, m, eps):
     T = h.shape[0]
     H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     pos = np.arange(T)
-    q = short_conv(h @ P["q"].T + P["q.b"], P["q.conv"]).reshape(T, H, D)
-    k = short_conv(h @ P["k"].T + P["k.b"], P["k.conv"]).reshape(T, G, D)
-    v = short_conv(h @ P["v"].T + P["v.b"], P["v.conv"]).reshape(T, G, V)
-    q = rotate_half(q, pos, m["rot"]["base"], m["rot"]["dims"])
-    k = rotate_half(k, pos, m["rot"]["base"], m["rot"]["dims"])
-    cap, size = m["softcap"], m["mask"]["size"]
-    dist = pos[:, None] - pos[None, :]
-    seen = (dist >= 0) & (dist < size)
-    out = np.zeros((T, H, V))
-    for head in range(H):
-        g = head // (H // G)
-        s = (q[:, head] @ k[:, g].T) * m["scale"]
-        s = cap * np.tanh(s / cap)
-        s = np.where(seen, s, -np.inf)
-        p = np.exp(s - s.max(-1, keepdims=True))
-        p = p / p.sum(-1, keepdims=True)
-        out[:, head] = p @ v[:, g]
+    q, k, v = (h @ P[n].T + P[n + ".b"] for n in "qkv")
+    if m["conv"]:
+        q, k, v = (short_conv(x, P[n + ".conv"]) for x, n in ((q, "q"), (k, "k"), (v, "v")))
+    q = rotate_half(q.reshape(T, H, D), pos, m["rot"]["base"], m["rot"]["dims"])
+    k = rotate_half(k.reshape(T, G, D), pos, m["rot"]["base"], m["rot"]["dims"])
+    out = capped_attention(q, k, v.reshape(T, G, V), pos, pos, m["scale"], m["softcap"], m["mask"]["size"])
     out = out.reshape(T, H * V) * sigmoid(h @ P["g"].T)
     return out @ P["o"].T
 
@@ -131,14 +164,7 @@ def ssd_mixer(h, P, m, eps):
     x = xbc[:, :inner].reshape(T, H, V)
     B = xbc[:, inner:inner + G * N].reshape(T, G, N)
     C = xbc[:, inner + G * N:].reshape(T, G, N)
-    y = np.zeros((T, H, V))
-    for head in range(H):
-        g = head // (H // G)
-        rate = np.exp(P["A_log"][head])
-        S = np.zeros((N, V))
-        for t in range(T):
-            S = np.exp(-rate * dt[t, head]) * S + dt[t, head] * np.outer(B[t, g], x[t, head])
-            y[t, head] = S.T @ C[t, g] + P["D"][head] * x[t, head]
+    y, _ = ssd_scan(x, B, C, dt, np.exp(P["A_log"]), P["D"])
     y = y.reshape(T, inner) * silu(z)
     y = rms_scale(y.reshape(T, parts, inner // parts), eps).reshape(T, inner) * P["norm"]
     return y @ P["o"].T
@@ -181,3 +207,44 @@ def forward(config, tensors, tokens, return_layers=False):
         layers.append(x.copy())
     logits = (offset_norm(x, tensors["final.norm"], eps) @ tensors["head"].T) * config["logit_scale"]
     return (logits, np.stack(layers)) if return_layers else logits
+
+
+def load_folder(folder):
+    """(config.json object, {tensor name: float64 array}) of a model folder; the safetensors file
+    is read here, by hand: 8 bytes of header length, the JSON header, then the data."""
+    import json
+    import os
+    import struct
+    with open(os.path.join(folder, "config.json")) as f:
+        config = json.load(f)
+    with open(os.path.join(folder, "model.safetensors"), "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(n))
+        data = f.read()
+    tensors = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        lo, hi = info["data_offsets"]
+        raw = data[lo:hi]
+        if info["dtype"] == "BF16":
+            a = (np.frombuffer(raw, dtype="<u2").astype(np.uint32) << 16).view(np.float32)
+        elif info["dtype"] == "F32":
+            a = np.frombuffer(raw, dtype="<f4")
+        else:
+            raise ValueError(f"{name}: dtype {info['dtype']}")
+        tensors[name] = a.astype(np.float64).reshape(info["shape"])
+    return config, tensors
+
+
+def generate(config, tensors, prompt, n, stop=()):
+    """Greedy continuation: (tokens, reason); the first largest logit wins; a stop token ends the
+    run and is the last token returned."""
+    toks, out = list(prompt), []
+    for _ in range(n):
+        nxt = int(np.argmax(forward(config, tensors, toks)[-1]))
+        out.append(nxt)
+        if nxt in stop:
+            return out, "stop"
+        toks.append(nxt)
+    return out, "length"

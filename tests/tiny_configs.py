@@ -108,3 +108,63 @@ TORETAR_C = {
         _toretar_layer(2, 16, 16, 16, 64, 0.2, 300000.0, 8, None),
     ],
 }
+
+
+def _kuporax_left(heads, kv_heads, dim, vdim, conv, scale, softcap, size, base, dims):
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "scale": scale, "softcap": softcap,
+            "mask": {"size": size}, "rot": {"base": base, "dims": dims}}
+
+
+def _kuporax_right(heads, vdim, state, groups, norm_groups, conv):
+    return {"heads": heads, "vdim": vdim, "state": state, "groups": groups, "norm_groups": norm_groups, "conv": conv}
+
+
+def _kuporax_parallel(left, right, left_scale, right_scale, ff):
+    return {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": left_scale, "right_scale": right_scale},
+            "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def _kuporax_delta(heads, kv_heads, dim, vdim, conv, ff):
+    return {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv},
+            "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+# Kuporax: four layers that differ in every size.  The first starts with the side-by-side mixer
+# (values wider than keys, part of each head rotated, a window of 50); the second is a delta layer
+# with as many q/k heads as heads and no feed-forward; the third has values narrower than keys, a
+# filter of one tap, every dimension rotated, a window of 9 and as many groups as heads; the fourth
+# has values that take two warps and a filter of five taps.  Nothing is a power of two by design.
+KUPORAX_A = {
+    "architecture": "Kuporax", "vocab": 211, "width": 72, "max_positions": 600, "logit_scale": 1.7, "norm": {"eps": 1e-5},
+    "layers": [
+        _kuporax_parallel(_kuporax_left(4, 2, 24, 40, 2, 0.19, 7.5, 50, 10000.0, 16), _kuporax_right(3, 16, 12, 1, 3, 3),
+                          0.6, 1.3, 96),
+        _kuporax_delta(4, 4, 16, 24, 3, 0),
+        _kuporax_parallel(_kuporax_left(3, 3, 32, 16, 1, 0.25, 11.0, 9, 300.0, 32), _kuporax_right(4, 8, 20, 4, 1, 2),
+                          1.0, 0.5, 40),
+        _kuporax_delta(6, 2, 8, 40, 5, 64),
+    ],
+}
+
+# Kuporax with sizes the tensor-core products take and heads as wide as released models have:
+# a window that spans pages, keys of 64 with values of 128, a state of 64, and a width that makes
+# every product's inner size a multiple of 8; a logit scale of one; a layer without rotation.
+KUPORAX_B = {
+    "architecture": "Kuporax", "vocab": 520, "width": 128, "max_positions": 1024, "logit_scale": 1.0, "norm": {"eps": 1e-6},
+    "layers": [
+        _kuporax_delta(4, 2, 64, 64, 4, 192),
+        _kuporax_parallel(_kuporax_left(8, 2, 64, 128, 4, 0.125, 30.0, 130, 500000.0, 32), _kuporax_right(4, 32, 64, 2, 2, 4),
+                          0.9, 1.2, 192),
+        _kuporax_parallel(_kuporax_left(2, 1, 48, 80, 3, 0.15, 50.0, 64, 1000.0, 0), _kuporax_right(2, 64, 16, 1, 1, 2),
+                          1.1, 0.7, 0),
+    ],
+}
+
+# A width that is no multiple of 8: in bfloat16 the products run on the plain kernel.
+KUPORAX_C = {
+    "architecture": "Kuporax", "vocab": 97, "width": 52, "max_positions": 300, "logit_scale": 0.5, "norm": {"eps": 1e-6},
+    "layers": [
+        _kuporax_delta(2, 1, 12, 20, 2, 36),
+        _kuporax_parallel(_kuporax_left(2, 2, 20, 12, 2, 0.3, 5.0, 17, 50.0, 4), _kuporax_right(2, 10, 6, 2, 2, 3), 1.5, 0.8, 0),
+    ],
+}
