@@ -43,7 +43,7 @@ def short_conv(u, taps, bias=None):
     T, C = u.shape
     K = taps.shape[1]
     y = np.zeros((T, C))
-    for d in range(K):
+    for d in range(min(K, T)):
         y[d:] += u[:T - d] * taps[:, K - 1 - d]
     if bias is not None:
         y = y + bias
