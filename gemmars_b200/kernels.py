@@ -1512,11 +1512,30 @@ def filter_rope_cache(u, taps, state, inv_freq, rot, ctx_pos, tok_seq, seq_slot,
            2 * u.numel() * u.element_size())
 
 
+#: whether bfloat16 steps take the tensor-core kernel where its sizes allow (tests turn it off to
+#: run the plain kernel on the same inputs)
+CAPPED_ATTENTION_MMA = True
+
+
+def attention_capped_mma_usable(dtype, dim: int, vdim: int, page_size: int) -> bool:
+    return (dtype == torch.bfloat16 and dim % 16 == 0 and 16 <= dim <= 256 and vdim % 8 == 0 and 8 <= vdim <= 256
+            and page_size % 32 == 0)
+
+
+def attention_capped_units(compute: str, dim: int, vdim: int, page_size: int = 64):
+    units = [("attention_capped", ())]
+    if compute == "bfloat16" and attention_capped_mma_usable(torch.bfloat16, dim, vdim, page_size):
+        units.append(("attention_capped_mma", (("GB_HEAD_DIM", dim), ("GB_VALUE_DIM", vdim))))
+    return units
+
+
 def attention_capped(ctx, q, out, heads, kcache, vcache, page_table, page_size, window, scale, cap, gate=None,
                      out_scale: float = 1.0):
     """Attention of the step's queries [T, heads * dim] over the cache with keys of ``dim`` and
     values of ``vdim``: score = (q . k) * scale, capped as cap * tanh(score / cap) when ``cap``;
-    a window of ``window`` keys when given; the output times sigmoid(gate) * out_scale."""
+    a window of ``window`` keys when given; the output times sigmoid(gate) * out_scale.  bfloat16
+    steps run on the tensor cores where the sizes allow (keys a multiple of 16, values of 8, up to
+    256), prompts and single tokens alike; float32 and other sizes run the plain kernel."""
     _cuda(q, out, kcache, vcache, page_table, gate)
     groups, dim, vdim = kcache.shape[1], kcache.shape[3], vcache.shape[2]
     qp, ldq = _cols(q)
@@ -1524,6 +1543,18 @@ def attention_capped(ctx, q, out, heads, kcache, vcache, page_table, page_size, 
     gp, ldg = _cols(gate) if gate is not None else (None, 0)
     assert q.dtype == out.dtype == kcache.dtype == vcache.dtype and (gate is None or gate.dtype == q.dtype)
     assert q.shape[1] == heads * dim and out.shape[1] == heads * vdim
+    if (CAPPED_ATTENTION_MMA and attention_capped_mma_usable(q.dtype, dim, vdim, page_size)
+            and getattr(ctx, "cu_seqlens", None) is not None and qp % 16 == 0 and ldq % 8 == 0 and op % 4 == 0
+            and ldo % 2 == 0 and (gp or 0) % 4 == 0 and ldg % 2 == 0):
+        f = _fn("attention_capped_mma", "gb_attention_capped_mma",
+                [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_longlong, c_float,
+                 c_void_p], (("GB_HEAD_DIM", dim), ("GB_VALUE_DIM", vdim)))
+        _check(f(qp, ldq, op, ldo, kcache.data_ptr(), vcache.data_ptr(), page_table.data_ptr(), page_table.shape[1], page_size,
+                 groups, dim, vdim, ctx.cu_seqlens.data_ptr(), ctx.seq_start.data_ptr(), ctx.seq_slot.data_ptr(), ctx.n_seqs,
+                 q.shape[0], heads, int(window or 0), scale, float(cap or 0.0), gp, ldg, out_scale, _stream()),
+               "attention_capped_mma", "attention", 2 * q.numel() * q.element_size())
+        return
     f = _fn("attention_capped", "gb_attention_capped",
             [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_longlong, c_float, c_void_p])

@@ -11,7 +11,8 @@ For one token, with h the mixer's input:
 
 Keys (filtered and rotated) and values (filtered) live in the paged cache that every attention
 of the package uses (a window's pages are a ring); the filter's last ``conv`` - 1 inputs are a
-state per sequence.  Scores, softmax, angles and the gate are float32.  Parameters: hidden_size,
+state per sequence.  Scores, softmax, angles and the gate are float32.  bfloat16 steps run on
+the tensor cores where the head sizes allow (kernels.attention_capped).  Parameters: hidden_size,
 heads, kv_heads, dim, vdim, bias, conv, window, scale, softcap, gate, position, out_scale.
 """
 from __future__ import annotations
@@ -81,7 +82,7 @@ class CappedAttention(Part):
             self.filter = torch.cat([t["q_conv"], t["k_conv"], t["v_conv"]], dim=0).contiguous()
 
     def kernel_units(self):
-        return (kernels.gemm_units(self.compute) + [("attention_capped", ())]
+        return (kernels.gemm_units(self.compute) + kernels.attention_capped_units(self.compute, self.dim, self.vdim)
                 + ([("recurrent", ())] if self.taps > 1 else []))
 
     def cache_needs(self):

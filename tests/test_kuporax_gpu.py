@@ -237,10 +237,13 @@ def test_gated_norm_over_groups(dtype, n, group, wn, first):
 
 
 class _Ctx:
-    """What attention_capped reads of a step's context."""
+    """What attention_capped reads of a step's context: every query a sequence of its own that
+    brings one token, all of them reading the same slot."""
 
-    def __init__(self, pos, seq, slot):
-        self.tok_pos, self.tok_seq, self.seq_slot = pos, seq, slot
+    def __init__(self, positions, slot):
+        n = len(positions)
+        self.tok_pos, self.tok_seq, self.seq_slot = _i32(positions), _i32(np.arange(n)), _i32([slot] * n)
+        self.cu_seqlens, self.seq_start, self.n_seqs = _i32(np.arange(n + 1)), _i32(positions), n
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -316,13 +319,24 @@ def test_capped_attention_finds_planted_keys(dtype, heads, groups, dim, vdim, ro
     q = torch.from_numpy(qn.reshape(len(targets), -1)).to(dt).to(DEV)
     gate, gn = _rand(rng, (len(targets), heads * vdim + 2), dt)
     out = torch.empty((len(targets), heads * vdim), dtype=dt, device=DEV)
-    ctx = _Ctx(_i32([p for p, _ in targets]), _i32([0] * len(targets)), _i32([0]))
-    kernels.attention_capped(ctx, q, out, heads, kc, vc, table, PAGE, window, scale, cap, gate[:, 1:1 + heads * vdim], 0.7)
+    ctx = _Ctx([p for p, _ in targets], 0)
+    gate_cols = gate[:, 2:2 + heads * vdim]
+    kernels.attention_capped(ctx, q, out, heads, kc, vc, table, PAGE, window, scale, cap, gate_cols, 0.7)
+    if kernels.attention_capped_mma_usable(dt, dim, vdim, PAGE):
+        # the tensor-core kernel ran; the plain kernel on the same inputs agrees with it
+        other = torch.empty_like(out)
+        kernels.CAPPED_ATTENTION_MMA = False
+        try:
+            kernels.attention_capped(ctx, q, other, heads, kc, vc, table, PAGE, window, scale, cap, gate_cols, 0.7)
+        finally:
+            kernels.CAPPED_ATTENTION_MMA = True
+        assert not torch.equal(out, other)
+        assert (out.double() - other.double()).abs().max() < 2e-2 * max(1.0, float(other.abs().max()))
     kall = np.stack([keys[th[0, j // PAGE], :, j % PAGE] for j in range(n)])
     vall = np.stack([vc.double().cpu().numpy()[th[0, j // PAGE], :, :, j % PAGE] for j in range(n)])
     want = plain.capped_attention(q.double().cpu().numpy().reshape(len(targets), heads, dim), kall, vall, [p for p, _ in targets],
                                   np.arange(n), scale, cap, window)
-    want = want.reshape(len(targets), -1) * plain.sigmoid(gn[:, 1:1 + heads * vdim]) * 0.7
+    want = want.reshape(len(targets), -1) * plain.sigmoid(gn[:, 2:2 + heads * vdim]) * 0.7
     assert np.abs(out.double().cpu().numpy() - want).max() < (2e-5 if dtype == "float32" else 2e-2) * max(1.0, np.abs(want).max())
     if cap == 0.0 or cap >= 30.0:
         # the planted key decides: outside the window the output is never its value; inside it is,
@@ -330,7 +344,7 @@ def test_capped_attention_finds_planted_keys(dtype, heads, groups, dim, vdim, ro
         # says which)
         found = 0
         for i, (p, j) in enumerate(targets):
-            mine = vall[j].repeat(heads // groups, axis=0).reshape(-1) * plain.sigmoid(gn[i, 1:1 + heads * vdim]) * 0.7
+            mine = vall[j].repeat(heads // groups, axis=0).reshape(-1) * plain.sigmoid(gn[i, 2:2 + heads * vdim]) * 0.7
             close = np.abs(out[i].double().cpu().numpy() - mine).max() < 0.1 * np.abs(mine).max()
             assert close == (np.abs(want[i] - mine).max() < 0.1 * np.abs(mine).max())
             if p - j >= size:
