@@ -2,7 +2,7 @@
 """Decode and prefill throughput of Qwen3-shaped models with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference] [--config 8b|4b|32b]
-    python bench.py --compare toretar [--sizes small,lite,mid] [--batch 8] [--context 4096]
+    python bench.py --compare toretar|kuporax [--sizes small,lite,mid] [--batch 8] [--context 4096]
 
 ``--config 8b`` (the default) is the headline benchmark.  A step is one decode step of a batch
 of 8 sequences at a context of 8,192 tokens.  One JSON line is printed: ``value`` = decoded
@@ -124,7 +124,14 @@ def decode_bytes(model, runner, lengths):
         for part in block.parts().values():
             if hasattr(part, "decode_bytes"):
                 extra += part.decode_bytes(len(lengths)) - part.weight_bytes()
-    return model.weight_bytes() + extra + kv
+    # a fixed-size state per sequence (a recurrent mixer's) is read and written once a step
+    state = 0
+    for g in runner.cache.state_groups:
+        per_seq = g.data.element_size() * g.data.shape[0]
+        for n in g.need.shape:
+            per_seq *= n
+        state += 2 * per_seq * len(lengths)
+    return model.weight_bytes() + extra + kv + state
 
 
 def prefill_flops(cfg, t):
@@ -160,6 +167,34 @@ def toretar_prefill_flops(cfg, t):
             if mlp.get("shared"):
                 per_token += 6 * w * mlp["shared"]["ff"]
         total += per_token * t + attention
+    return total + 2 * w * cfg["vocab"]
+
+
+def kuporax_prefill_flops(cfg, t):
+    """Floating-point operations of a prompt of ``t`` tokens from position 0: every product, the
+    attention's scores and weighted values over the keys a window lets a token see, and the
+    recurrences as they are written (delta rule: two reads of the state and one update a token,
+    6 dim vdim a head; state space: one update and one read, 4 state vdim a head)."""
+    w, total = cfg["width"], 0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "delta":
+            qk, hv = m["kv_heads"] * m["dim"], m["heads"] * m["vdim"]
+            per_token = 2 * w * (2 * qk + 2 * hv + 2 * m["heads"]) + 2 * hv * w + 6 * m["heads"] * m["dim"] * m["vdim"]
+            pairs = 0
+        else:
+            a, r = m["left"], m["right"]
+            size = a["mask"]["size"]
+            seen = sum(min(p + 1, size) for p in range(t))
+            pairs = 2 * a["heads"] * (a["dim"] + a["vdim"]) * seen
+            inner = r["heads"] * r["vdim"]
+            per_token = (2 * w * ((a["heads"] + a["kv_heads"]) * a["dim"] + a["kv_heads"] * a["vdim"] + a["heads"] * a["vdim"])
+                         + 2 * a["heads"] * a["vdim"] * w
+                         + 2 * w * (2 * inner + 2 * r["groups"] * r["state"] + r["heads"]) + 2 * inner * w
+                         + 4 * r["heads"] * r["state"] * r["vdim"])
+        if layer.get("mlp") is not None:
+            per_token += 6 * w * layer["mlp"]["ff"]
+        total += per_token * t + pairs
     return total + 2 * w * cfg["vocab"]
 
 
@@ -251,7 +286,15 @@ def time_prefill(eng, cfg, tokens, tflops, tflops_sustained):
             pre_ms.append(e0.elapsed_time(e1))
         runner.close(s)
     pre = statistics.median(pre_ms)
-    flops = toretar_prefill_flops(cfg, tokens) if "layers" in cfg else prefill_flops(cfg, tokens)
+    if cfg.get("architecture") == "Kuporax":
+        flops = kuporax_prefill_flops(cfg, tokens)
+    elif cfg.get("sliding_window") and cfg.get("use_sliding_window"):
+        size = cfg["sliding_window"]      # a window on every layer: the keys a token sees, not the causal half
+        seen = sum(min(p + 1, size) for p in range(tokens))
+        flops = (prefill_flops(cfg, tokens) + cfg["num_hidden_layers"] * 4 * cfg["num_attention_heads"] * cfg["head_dim"]
+                 * (seen - tokens * (tokens + 1) // 2))
+    else:
+        flops = toretar_prefill_flops(cfg, tokens) if "layers" in cfg else prefill_flops(cfg, tokens)
     frac = flops / (pre / 1e3) / (tflops * 1e12)
     return {"value": round(tokens / (pre / 1e3), 1), "tokens": tokens, "ms": round(pre, 3), "frac": round(frac, 4),
             # a prompt is tens of milliseconds of products under the power cap: also against the sustained rate
@@ -437,13 +480,14 @@ def kernel_table(eng, tokens, batch, context):
 def run_compare(args):
     """Prompt and decode throughput of Toretar-shaped models beside Qwen3-shaped models of the same
     width, depth and per-token feed-forward size, with a table of each one's kernels."""
-    from gemmars_b200.tuning import PAIRS
+    from gemmars_b200.tuning import KUPORAX_PAIRS, PAIRS
+    pairs = KUPORAX_PAIRS if args.compare == "kuporax" else PAIRS
     hbm_gbs, tflops, tflops_sustained, peak_src = peaks()
     sizes = [s for s in args.sizes.split(",") if s]
     out = {}
     for size in sizes:
         out[size] = {}
-        for arch, cfg in zip(("toretar", "qwen3"), PAIRS[size]):
+        for arch, cfg in zip((args.compare, "qwen3"), pairs[size]):
             eng = make_engine(cfg, args.batch, args.batch * (args.context + 64) + PREFILL_TOKENS + 64, args.options)
             rec = {"prefill": time_prefill(eng, cfg, PREFILL_TOKENS, tflops, tflops_sustained),
                    "decode": time_decode(eng, args.batch, args.context, args.steps, max(3, args.warmup), False, hbm_gbs)}
@@ -455,7 +499,7 @@ def run_compare(args):
             import torch
             gc.collect()
             torch.cuda.empty_cache()
-    return {"compare": "toretar beside qwen3", "sizes": out, "batch": args.batch, "context": args.context,
+    return {"compare": f"{args.compare} beside qwen3", "sizes": out, "batch": args.batch, "context": args.context,
             "prefill_tokens": PREFILL_TOKENS, "peaks": f"{hbm_gbs:.0f} GB/s, {tflops:.0f} TFLOP/s ({peak_src})",
             "dtype": "bf16", "data": "synthetic: random weights, random token ids, cache filled with random rows"}
 
@@ -476,8 +520,8 @@ def main():
     ap.add_argument("--e2e-tokens", type=int, default=E2E_TOKENS,
                     help="tokens a sequence generates in the end-to-end run (fewer for runs under a profiler)")
     ap.add_argument("--options", default="", help='further engine options, "key=value;key=value"')
-    ap.add_argument("--compare", choices=["toretar"], default=None,
-                    help="instead of the headline: Toretar-shaped models beside Qwen3-shaped ones of equal size")
+    ap.add_argument("--compare", choices=["toretar", "kuporax"], default=None,
+                    help="instead of the headline: models of that architecture beside Qwen3-shaped ones of equal size")
     ap.add_argument("--sizes", default="small,lite,mid", help="with --compare: which pairs of tuning.PAIRS")
     args = ap.parse_args()
     if args.impl == "reference":

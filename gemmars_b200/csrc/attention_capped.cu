@@ -30,52 +30,47 @@ __device__ __forceinline__ float filtered(const T* __restrict__ u, long long ldu
   return acc;
 }
 
+// One block per (token, head): the H query heads, then the G key heads, then the G value heads.
 template <typename T>
-__global__ void __launch_bounds__(256) filter_rope_cache_kernel(
+__global__ void __launch_bounds__(128) filter_rope_cache_kernel(
     const T* __restrict__ u, long long ldu, const float* __restrict__ taps, const float* __restrict__ state, int K,
     const float* __restrict__ inv_freq, int rot, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
     const int* __restrict__ seq_slot, const int* __restrict__ cu, const int* __restrict__ page_table, int table_width,
     int page_size, T* __restrict__ q_out, long long ldq, T* __restrict__ kcache, T* __restrict__ vcache, int H, int G, int D,
     int Vd) {
-  extern __shared__ float cs[];   // cos[rot/2], sin[rot/2]
   pdl_release_next();
   pdl_wait_prior();
-  const int t = blockIdx.x, b = tok_seq[t], pos = tok_pos[t], slot = seq_slot[b];
+  const int t = blockIdx.x, hh = blockIdx.y, b = tok_seq[t], pos = tok_pos[t], slot = seq_slot[b];
   const int row0 = cu[b], local = t - row0, half = rot / 2;
   const int C = (H + G) * D + G * Vd;
   const float* hist = K > 1 ? state + (size_t)slot * (K - 1) * C : nullptr;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    float s, c;
-    sincosf((float)pos * inv_freq[i], &s, &c);
-    cs[i] = c;
-    cs[half + i] = s;
-  }
-  __syncthreads();
   const int page = page_table ? page_table[(size_t)slot * table_width + (pos / page_size) % table_width] : 0;
   const int off = pos % page_size;
-  for (int e = threadIdx.x; e < (H + G) * D; e += blockDim.x) {
-    const int hh = e / D, i = e - hh * D;
+  if (hh >= H + G) {                  // a value head: filtered, then into its page (a dim's positions contiguous)
+    if (!vcache) return;
+    const int g = hh - H - G;
+    for (int d = threadIdx.x; d < Vd; d += blockDim.x) {
+      const int c = (H + G) * D + g * Vd + d;
+      const float val = K > 1 ? filtered(u, ldu, row0, local, hist, taps, C, c, K) : to_f32(u[(size_t)t * ldu + c]) * (K == 1 ? taps[c] : 1.f);
+      vcache[(((size_t)page * G + g) * Vd + d) * page_size + off] = from_f32<T>(val);
+    }
+    return;
+  }
+  if (hh >= H && !kcache) return;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const int e = hh * D + i;
     float val = K > 1 ? filtered(u, ldu, row0, local, hist, taps, C, e, K) : to_f32(u[(size_t)t * ldu + e]) * (K == 1 ? taps[e] : 1.f);
     if (i < rot) {
       const int j = i < half ? i : i - half, partner = i < half ? e + half : e - half;
       const float other = K > 1 ? filtered(u, ldu, row0, local, hist, taps, C, partner, K)
                                 : to_f32(u[(size_t)t * ldu + partner]) * (K == 1 ? taps[partner] : 1.f);
+      float sn, cs;
+      sincosf((float)pos * inv_freq[j], &sn, &cs);
       // (a, b) -> (a cos - b sin, b cos + a sin)
-      val = i < half ? val * cs[j] - other * cs[half + j] : val * cs[j] + other * cs[half + j];
+      val = i < half ? val * cs - other * sn : val * cs + other * sn;
     }
-    if (hh < H) {
-      q_out[(size_t)t * ldq + e] = from_f32<T>(val);
-    } else if (kcache) {
-      const int g = hh - H;
-      kcache[(((size_t)page * G + g) * page_size + off) * D + i] = from_f32<T>(val);
-    }
-  }
-  if (vcache) {
-    for (int e = threadIdx.x; e < G * Vd; e += blockDim.x) {
-      const int c = (H + G) * D + e, g = e / Vd, d = e - g * Vd;
-      const float val = K > 1 ? filtered(u, ldu, row0, local, hist, taps, C, c, K) : to_f32(u[(size_t)t * ldu + c]) * (K == 1 ? taps[c] : 1.f);
-      vcache[(((size_t)page * G + g) * Vd + d) * page_size + off] = from_f32<T>(val);
-    }
+    if (hh < H) q_out[(size_t)t * ldq + e] = from_f32<T>(val);
+    else kcache[(((size_t)page * G + (hh - H)) * page_size + off) * D + i] = from_f32<T>(val);
   }
 }
 
@@ -88,13 +83,13 @@ GB_EXPORT int gb_filter_rope_cache(const void* u, int dtype, long long ldu, cons
   if (ntok <= 0) return 0;
   if (K < 0 || K > MAX_TAPS || rot < 0 || rot > D || rot % 2 || H <= 0 || G <= 0 || D <= 0 || Vd <= 0) return GB_ERR_SIZE;
   if ((K > 0 && !taps) || (K > 1 && !state) || (rot > 0 && !inv_freq)) return GB_ERR_ARG;
-  const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
+  const dim3 grid(ntok, H + 2 * G);
   if (dtype == GB_F32)
-    gb_launch(filter_rope_cache_kernel<float>, ntok, 256, smem, stream, (const float*)u, ldu, taps, state, K, inv_freq, rot,
+    gb_launch(filter_rope_cache_kernel<float>, grid, 128, 0, stream, (const float*)u, ldu, taps, state, K, inv_freq, rot,
               tok_pos, tok_seq, seq_slot, cu, page_table, table_width, page_size, (float*)q_out, ldq, (float*)kcache,
               (float*)vcache, H, G, D, Vd);
   else if (dtype == GB_BF16)
-    gb_launch(filter_rope_cache_kernel<bf16>, ntok, 256, smem, stream, (const bf16*)u, ldu, taps, state, K, inv_freq, rot,
+    gb_launch(filter_rope_cache_kernel<bf16>, grid, 128, 0, stream, (const bf16*)u, ldu, taps, state, K, inv_freq, rot,
               tok_pos, tok_seq, seq_slot, cu, page_table, table_width, page_size, (bf16*)q_out, ldq, (bf16*)kcache,
               (bf16*)vcache, H, G, D, Vd);
   else

@@ -7,7 +7,8 @@
 // tokens of one sequence for one query head, each row masked at its own position and window;
 // keys (contiguous in the dims) and values (contiguous in the positions) feed the MMAs straight
 // from the paged cache; a CTA covers 64 tokens of one sequence and up to two query heads that
-// share a kv head.  A step of single tokens is the same with one live row a warp.  Scores,
+// share a kv head.  In a step of single tokens the warps of a head share the sequence's keys
+// instead, every fourth block each, and their parts are added in warp order.  Scores,
 // the cap, the softmax and the gate are float32; tanh is the hardware's approximation
 // (tanh.approx.f32, relative error about 2^-11), which is below what bfloat16 operands leave.
 #include "mma.cuh"
@@ -43,7 +44,7 @@ attention_capped_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16
                          const bf16* __restrict__ kcache, const bf16* __restrict__ vcache, PagedKV kv,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_slot, int n_seqs, int nh, int window, int heads_per_cta, float scale,
-                         float cap, const bf16* __restrict__ gate, long long gate_stride, float out_scale) {
+                         float cap, const bf16* __restrict__ gate, long long gate_stride, float out_scale, int single) {
   pdl_release_next();
   pdl_wait_prior();
   // ---- which sequence and which 64-token tile of it
@@ -61,11 +62,16 @@ attention_capped_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16
   const int chunks = (rep + heads_per_cta - 1) / heads_per_cta;
   const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
   const int hl = chunk * heads_per_cta + hr;          // head within the kv group
-  if (hl >= rep) return;
-  const int head = kvh * rep + hl;
+  // A step of single tokens (``single``): a sequence's one row is worked by all MT warps of its
+  // head, each taking every MT-th block of keys; their parts meet in shared memory at the end,
+  // so no warp leaves before that.
+  __shared__ float part_m[RH][MT], part_l[RH][MT], part_o[RH][MT][VD];
+  const bool idle = hl >= rep;
+  if (idle && !single) return;
+  const int head = kvh * rep + (idle ? 0 : hl);
   const int seq_len = cu_seqlens[b + 1] - cu_seqlens[b];
-  const int first = tile * TILE + mt * 16;            // first token of this warp within the sequence's step
-  if (first >= seq_len) return;
+  const int first = single ? 0 : tile * TILE + mt * 16;   // first token of this warp within the sequence's step
+  if (first >= seq_len && !single) return;
   const int slot = seq_slot[b], start = seq_start[b];
   const int tok0 = cu_seqlens[b] + first;
   const bool v0 = first + g < seq_len, v1 = first + g + 8 < seq_len;
@@ -100,7 +106,7 @@ attention_capped_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16
   for (int d = 0; d < VD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
   const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f, cap2 = cap * LOG2E, scale2 = scale * LOG2E;
-  for (int blk = lo_first / KEYS; blk * KEYS <= last; ++blk) {
+  for (int blk = lo_first / KEYS + (single ? mt : 0); blk * KEYS <= last && !idle; blk += single ? MT : 1) {
     const int key0 = blk * KEYS;
     const int page = kv.page_table[(size_t)slot * kv.table_width + (key0 / kv.page_size) % kv.table_width];
     const size_t page_base = ((size_t)page * kv.num_kv_heads + kvh) * kv.page_size * HD;
@@ -165,6 +171,40 @@ attention_capped_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16
   }
   l0 = quad_sum(l0);
   l1 = quad_sum(l1);
+  if (single) {
+    // row 0 (lanes 0..3 hold its columns 8 d + 2 c, + 1): the warps' parts, then warp mt = 0 adds them
+    if (g == 0 && !idle) {
+      if (c == 0) { part_m[hr][mt] = m0; part_l[hr][mt] = l0; }
+#pragma unroll
+      for (int d = 0; d < VD / 8; ++d) {
+        part_o[hr][mt][d * 8 + 2 * c] = o[d][0];
+        part_o[hr][mt][d * 8 + 2 * c + 1] = o[d][1];
+      }
+    }
+    __syncthreads();
+    if (mt != 0 || idle) return;
+    float top = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < MT; ++i) top = fmaxf(top, part_m[hr][i]);
+    float w[MT], total = 0.f;
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      w[i] = part_m[hr][i] == -INFINITY ? 0.f : exp2f(part_m[hr][i] - top);
+      total += w[i] * part_l[hr][i];
+    }
+    const float inv = out_scale / total;
+    bf16* dst = out + (size_t)tok0 * out_stride + (size_t)head * VD;
+    const bf16* gt = gate ? gate + (size_t)tok0 * gate_stride + (size_t)head * VD : nullptr;
+    for (int col = lane; col < VD; col += 32) {
+      float a = 0.f;
+#pragma unroll
+      for (int i = 0; i < MT; ++i) a = fmaf(w[i], part_o[hr][i][col], a);
+      a *= inv;
+      if (gt) a *= 1.0f / (1.0f + __expf(-__bfloat162float(gt[col])));
+      dst[col] = __float2bfloat16_rn(a);
+    }
+    return;
+  }
   if (v0) {
     const float inv = out_scale / l0;
     bf16* dst = out + (size_t)(tok0 + g) * out_stride + (size_t)head * VD + 2 * c;
@@ -206,7 +246,7 @@ GB_EXPORT int gb_attention_capped_mma(const void* q, long long q_stride, void* o
                                       const void* kcache, const void* vcache, const int* page_table, int table_width,
                                       int page_size, int nkv, int hd, int vd, const int* cu_seqlens, const int* seq_start,
                                       const int* seq_slot, int n_seqs, int ntok, int nh, int window, float scale, float cap,
-                                      const void* gate, long long gate_stride, float out_scale, cudaStream_t stream) {
+                                      const void* gate, long long gate_stride, float out_scale, int single, cudaStream_t stream) {
   if (ntok <= 0 || n_seqs <= 0) return 0;
   if (hd != HD || vd != VD || nkv <= 0 || nh % nkv || page_size % KEYS) return GB_ERR_SIZE;
   if (((uintptr_t)q & 15) || (q_stride % 8) || ((uintptr_t)out & 3) || (out_stride % 2) || ((uintptr_t)kcache & 15) ||
@@ -216,9 +256,11 @@ GB_EXPORT int gb_attention_capped_mma(const void* q, long long q_stride, void* o
   const int rep = nh / nkv;
   const int heads_per_cta = rep < RH ? rep : RH;
   const int chunks = (rep + heads_per_cta - 1) / heads_per_cta;
-  dim3 grid((ntok + TILE - 1) / TILE + n_seqs, nkv * chunks);
+  // single: every sequence brings one token (ntok == n_seqs), one tile a sequence
+  if (single && ntok != n_seqs) return GB_ERR_ARG;
+  dim3 grid(single ? n_seqs : (ntok + TILE - 1) / TILE + n_seqs, nkv * chunks);
   gb_launch(attention_capped_mma_kernel, grid, MT * heads_per_cta * 32, 0, stream,
       (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, kv, cu_seqlens,
-      seq_start, seq_slot, n_seqs, nh, window, heads_per_cta, scale, cap, (const bf16*)gate, gate_stride, out_scale);
+      seq_start, seq_slot, n_seqs, nh, window, heads_per_cta, scale, cap, (const bf16*)gate, gate_stride, out_scale, single);
   return gb_launch_status();
 }

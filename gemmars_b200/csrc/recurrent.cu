@@ -107,211 +107,272 @@ GB_EXPORT int gb_short_filter_state(const void* u, int in_dtype, long long ldu, 
   return gb_launch_status();
 }
 
-// Sums of up to three values over the block, the same in every thread.  One warp: shuffles alone.
-__device__ __forceinline__ void block_sum3(float& a, float& b, float& c, float* red /* 3 * 32 */) {
-  a = warp_sum(a); b = warp_sum(b); c = warp_sum(c);
-  const int nwarp = (blockDim.x + 31) >> 5;
-  if (nwarp == 1) return;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane == 0) { red[warp * 3] = a; red[warp * 3 + 1] = b; red[warp * 3 + 2] = c; }
-  __syncthreads();
-  a = b = c = 0.f;
-  for (int w = 0; w < nwarp; ++w) { a += red[w * 3]; b += red[w * 3 + 1]; c += red[w * 3 + 2]; }
-}
-
 // ------------------------------------------------------------------ gated delta rule
-// One block per (sequence, head); thread j owns column j of the head's state S [D, V] in shared
-// memory.  Per token, with k^ = k / sqrt(|k|^2 + 1e-6), q^ = q / sqrt(|q|^2 + 1e-6) * qscale,
+// The state of a head is a matrix S [dim, vdim].  A block is 32 columns of one (sequence, head);
+// a column is worked by P lanes side by side, each holding 32 of the column's dims in registers
+// (dim <= 32 P, zeros beyond).  In memory a head's state is kept in the order the lanes read it,
+// 16 bytes a lane and a warp's lanes side by side: element (d, col), d = 32 part + 4 r + e, lies at
+// ((r * vdim + col) * P + part) * 4 + e  (8 * vdim * P * 4 floats a head).
+// Per token, with k^ = k / sqrt(|k|^2 + 1e-6), q^ = q / sqrt(|q|^2 + 1e-6) * qscale,
 // beta = sigmoid(bl), g = exp(-exp(A_log) * softplus(al + dt_bias)):
 //   S <- g S;  u = beta (v - S^T k^);  S <- S + k^ u^T;  y = S^T q^
-// The two products with the old state are taken in one pass (y = g S_old^T q^ + (k^ . q^) u).
-// The next token's k, q and v are asked for before the current token is worked.
-constexpr int PREFETCH = 8;   // D <= PREFETCH * threads
+// The two products with the old state are taken in one pass (y = g S_old^T q^ + (k^ . q^) u) and
+// meet over the P lanes by shuffles.  Tokens come into shared memory eight at a time by
+// asynchronous copies, a group ahead of the one being worked; what does not depend on the state
+// (the norms of k and q, k . q, beta, the decay) is worked out for the whole group at once, a
+// token a warp, so that the walk from token to token is the state's arithmetic alone.
+constexpr int SLICE = 32;   // dims of a column that one lane holds
+constexpr int GROUP = 8;    // tokens brought in together
+// A lane's 32 dims of k, q, B or C start 36 floats after its neighbour's: the P lanes of a column
+// read their 16 bytes from different banks (128 bytes apart they would all hit the same four).
+__device__ __forceinline__ int padded(int i) { return i + (i >> 5) * 4; }
+constexpr int padded_size(int lanes) { return lanes * (SLICE + 4); }
 
-__global__ void delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
-                                  long long ld, const float* __restrict__ beta_logit, const float* __restrict__ a_logit,
-                                  long long ldg, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
-                                  float* __restrict__ state, const int* __restrict__ cu, const int* __restrict__ seq_slot,
-                                  float* __restrict__ y, int H, int G, int D, int V, float qscale) {
-  extern __shared__ float sm[];
-  float* S = sm;                 // [D][V]
-  float* kq = S + (size_t)D * V; // two buffers of k[D], q[D]
-  float* red = kq + 4 * D;       // 96
+template <int P>
+__device__ __forceinline__ float lanes_sum(float v) {
+#pragma unroll
+  for (int o = P / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ void copy_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int P>
+__global__ void __launch_bounds__(32 * P) delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k,
+                                                           const float* __restrict__ v, long long ld,
+                                                           const float* __restrict__ beta_logit, const float* __restrict__ a_logit,
+                                                           long long ldg, const float* __restrict__ A_log,
+                                                           const float* __restrict__ dt_bias, float* __restrict__ state,
+                                                           const int* __restrict__ cu, const int* __restrict__ seq_slot,
+                                                           float* __restrict__ y, int H, int G, int D, int V, float qscale) {
+  constexpr int DP = P * SLICE;
+  __shared__ __align__(16) float kq[2][GROUP][2][padded_size(P)];   // [buffer][token][k | q][dims, padded]
+  __shared__ float vs[2][GROUP][32], gates[2][GROUP][2];
+  __shared__ float pre[GROUP][4];                       // per token: decay, 1/|k|, beta, (k^ . q^); then decay * qscale/|q|
+  __shared__ float pre_q[GROUP];
   pdl_release_next();
   pdl_wait_prior();
-  const int b = blockIdx.x, head = blockIdx.y, g = head / (H / G), tid = threadIdx.x, nthr = blockDim.x;
+  const int b = blockIdx.x, head = blockIdx.y, g = head / (H / G), tid = threadIdx.x;
+  const int col = blockIdx.z * 32 + tid / P, part = tid % P, lane = tid & 31, warp = tid >> 5;
+  const bool live = col < V;
   const int t0 = cu[b], t1 = cu[b + 1];
-  float* Sg = state + ((size_t)seq_slot[b] * H + head) * D * V;
-  for (int i = tid; i < D * V; i += nthr) S[i] = Sg[i];
-  const float rate = expf(A_log[head]), dtb = dt_bias[head];
-  float v_next = 0.f, bl_next = 0.f, al_next = 0.f;
-  if (t0 < t1) {
-    for (int i = tid; i < D; i += nthr) {
-      kq[i] = k[(size_t)t0 * ld + g * D + i];
-      kq[D + i] = q[(size_t)t0 * ld + g * D + i];
-    }
-    if (tid < V) v_next = v[(size_t)t0 * ld + head * V + tid];
-    bl_next = beta_logit[(size_t)t0 * ldg + head];
-    al_next = a_logit[(size_t)t0 * ldg + head];
+  float4* Sg = (float4*)(state + ((size_t)seq_slot[b] * H + head) * 8 * V * P * 4);
+  float S[SLICE];
+#pragma unroll
+  for (int r = 0; r < SLICE / 4; ++r) {
+    const float4 s4 = live ? Sg[((size_t)r * V + col) * P + part] : make_float4(0.f, 0.f, 0.f, 0.f);
+    S[4 * r] = s4.x; S[4 * r + 1] = s4.y; S[4 * r + 2] = s4.z; S[4 * r + 3] = s4.w;
   }
-  __syncthreads();
-  for (int t = t0; t < t1; ++t) {
-    const int buf = (t - t0) & 1;
-    const float* ks = kq + buf * 2 * D;
-    const float* qs = ks + D;
-    const float v_cur = v_next, bl = bl_next, al = al_next;
-    float pk[PREFETCH], pq[PREFETCH];
-    if (t + 1 < t1) {
-#pragma unroll
-      for (int r = 0; r < PREFETCH; ++r) {
-        const int i = tid + r * nthr;
-        if (i < D) {
-          pk[r] = k[(size_t)(t + 1) * ld + g * D + i];
-          pq[r] = q[(size_t)(t + 1) * ld + g * D + i];
-        }
+  const float rate = expf(A_log[head]), dtb = dt_bias[head];
+  if (tid >= D)      // the dims beyond the head's are zeros, written once
+    for (int j = 0; j < 2 * GROUP; ++j) kq[j / GROUP][j % GROUP][0][padded(tid)] = kq[j / GROUP][j % GROUP][1][padded(tid)] = 0.f;
+  // every thread brings one dim of k and of q of every token of a group
+  auto bring = [&](int first, int buf) {
+    for (int j = 0; j < GROUP && first + j < t1; ++j) {
+      const size_t t = first + j;
+      if (tid < D) {
+        copy_async4(&kq[buf][j][0][padded(tid)], k + t * ld + g * D + tid);
+        copy_async4(&kq[buf][j][1][padded(tid)], q + t * ld + g * D + tid);
       }
-      if (tid < V) v_next = v[(size_t)(t + 1) * ld + head * V + tid];
-      bl_next = beta_logit[(size_t)(t + 1) * ldg + head];
-      al_next = a_logit[(size_t)(t + 1) * ldg + head];
+      if (live && part == 0) copy_async4(&vs[buf][j][tid / P], v + t * ld + head * V + col);
+      if (tid == 0) copy_async4(&gates[buf][j][0], beta_logit + t * ldg + head);
+      if (tid == 1) copy_async4(&gates[buf][j][1], a_logit + t * ldg + head);
     }
-    float kk = 0.f, qq = 0.f, kdq = 0.f;
-    for (int i = tid; i < D; i += nthr) {
-      kk = fmaf(ks[i], ks[i], kk);
-      qq = fmaf(qs[i], qs[i], qq);
-      kdq = fmaf(ks[i], qs[i], kdq);
+    copy_async_commit();
+  };
+  bring(t0, 0);
+  for (int first = t0; first < t1; first += GROUP) {
+    const int buf = ((first - t0) / GROUP) & 1;
+    if (first + GROUP < t1) {
+      bring(first + GROUP, buf ^ 1);
+      copy_async_wait<1>();
+    } else {
+      copy_async_wait<0>();
     }
-    block_sum3(kk, qq, kdq, red);
-    const float inv_k = 1.0f / sqrtf(kk + 1e-6f), inv_q = qscale / sqrtf(qq + 1e-6f);
-    const float beta = sigmoid_f(bl), decay = expf(-rate * softplus_f(al + dtb));
-    if (tid < V) {
-      float sk = 0.f, sq = 0.f;
-      for (int d = 0; d < D; ++d) {
-        const float s = S[d * V + tid];
-        sk = fmaf(s, ks[d], sk);
-        sq = fmaf(s, qs[d], sq);
+    __syncthreads();
+    const int n = min(GROUP, t1 - first);
+    for (int j = warp; j < n; j += P) {       // a token a warp: what the state has no part in
+      float kk = 0.f, qq = 0.f, kdq = 0.f;
+      for (int i = lane; i < DP; i += 32) {
+        const float kv = kq[buf][j][0][padded(i)], qv = kq[buf][j][1][padded(i)];
+        kk = fmaf(kv, kv, kk); qq = fmaf(qv, qv, qq); kdq = fmaf(kv, qv, kdq);
       }
-      const float u = beta * (v_cur - decay * inv_k * sk);
-      const float ku = inv_k * u;
-      for (int d = 0; d < D; ++d) S[d * V + tid] = fmaf(ks[d], ku, decay * S[d * V + tid]);
-      y[(size_t)t * H * V + head * V + tid] = fmaf(kdq * inv_k * inv_q, u, decay * inv_q * sq);
-    }
-    if (t + 1 < t1) {
-      float* nb = kq + (buf ^ 1) * 2 * D;
-#pragma unroll
-      for (int r = 0; r < PREFETCH; ++r) {
-        const int i = tid + r * nthr;
-        if (i < D) { nb[i] = pk[r]; nb[D + i] = pq[r]; }
+      kk = warp_sum(kk); qq = warp_sum(qq); kdq = warp_sum(kdq);
+      if (lane == 0) {
+        const float inv_k = 1.0f / sqrtf(kk + 1e-6f), inv_q = qscale / sqrtf(qq + 1e-6f);
+        const float decay = expf(-rate * softplus_f(gates[buf][j][1] + dtb));
+        pre[j][0] = decay; pre[j][1] = inv_k; pre[j][2] = sigmoid_f(gates[buf][j][0]); pre[j][3] = kdq * inv_k * inv_q;
+        pre_q[j] = decay * inv_q;
       }
     }
     __syncthreads();
+    for (int j = 0; j < n; ++j) {
+      const float4* ks = (const float4*)(kq[buf][j][0] + part * (SLICE + 4));
+      const float4* qs = (const float4*)(kq[buf][j][1] + part * (SLICE + 4));
+      float4 kheld[SLICE / 4];              // k is used twice: kept between the read and the write of S
+      float sk = 0.f, sk2 = 0.f, sq = 0.f, sq2 = 0.f;
+#pragma unroll
+      for (int r = 0; r < SLICE / 4; ++r) {
+        const float4 kv = kheld[r] = ks[r], qv = qs[r];
+        sk = fmaf(S[4 * r], kv.x, sk); sk2 = fmaf(S[4 * r + 1], kv.y, sk2); sk = fmaf(S[4 * r + 2], kv.z, sk); sk2 = fmaf(S[4 * r + 3], kv.w, sk2);
+        sq = fmaf(S[4 * r], qv.x, sq); sq2 = fmaf(S[4 * r + 1], qv.y, sq2); sq = fmaf(S[4 * r + 2], qv.z, sq); sq2 = fmaf(S[4 * r + 3], qv.w, sq2);
+      }
+      sk = lanes_sum<P>(sk + sk2);
+      sq = lanes_sum<P>(sq + sq2);
+      const float decay = pre[j][0], inv_k = pre[j][1];
+      const float u = pre[j][2] * ((live ? vs[buf][j][tid / P] : 0.f) - decay * inv_k * sk);
+      const float ku = inv_k * u;
+#pragma unroll
+      for (int r = 0; r < SLICE / 4; ++r) {
+        const float4 kv = kheld[r];
+        S[4 * r] = fmaf(kv.x, ku, decay * S[4 * r]);
+        S[4 * r + 1] = fmaf(kv.y, ku, decay * S[4 * r + 1]);
+        S[4 * r + 2] = fmaf(kv.z, ku, decay * S[4 * r + 2]);
+        S[4 * r + 3] = fmaf(kv.w, ku, decay * S[4 * r + 3]);
+      }
+      if (live && part == 0) y[(size_t)(first + j) * H * V + head * V + col] = fmaf(pre[j][3], u, pre_q[j] * sq);
+    }
+    __syncthreads();   // the group after next is brought into this buffer; pre is written again
   }
-  for (int i = tid; i < D * V; i += nthr) Sg[i] = S[i];
+  if (live) {
+#pragma unroll
+    for (int r = 0; r < SLICE / 4; ++r)
+      Sg[((size_t)r * V + col) * P + part] = make_float4(S[4 * r], S[4 * r + 1], S[4 * r + 2], S[4 * r + 3]);
+  }
 }
 
+static inline int lanes_for(int dims) { return dims <= SLICE ? 1 : (dims <= 2 * SLICE ? 2 : (dims <= 4 * SLICE ? 4 : 8)); }
+
+// Floats of one head's state for columns of ``dims`` (what a caller allocates per slot and head).
+GB_EXPORT int gb_state_floats(int dims, int V) { return 8 * V * lanes_for(dims) * 4; }
+
+// state: [slots, H, gb_state_floats(D, V)] float32, in the order described above.
 GB_EXPORT int gb_delta_rule(const float* q, const float* k, const float* v, long long ld, const float* beta_logit,
                             const float* a_logit, long long ldg, const float* A_log, const float* dt_bias, float* state,
                             const int* cu, const int* seq_slot, float* y, int nseq, int H, int G, int D, int V, float qscale,
                             cudaStream_t stream) {
   if (nseq <= 0) return 0;
-  int threads = ((V + 31) / 32) * 32;
-  if (G <= 0 || H % G || V <= 0 || threads > 1024 || D <= 0 || D > PREFETCH * threads) return GB_ERR_SIZE;
-  const size_t smem = ((size_t)D * V + 4 * D + 96) * sizeof(float);
-  if (smem > 200 * 1024) return GB_ERR_SIZE;
-  static bool raised = false;
-  if (!raised) {
-    cudaFuncSetAttribute(delta_rule_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    raised = true;
+  if (G <= 0 || H % G || V <= 0 || D <= 0 || D > 8 * SLICE || ((uintptr_t)state & 15)) return GB_ERR_SIZE;
+  dim3 grid(nseq, H, (V + 31) / 32);
+#define GB_DELTA(P)                                                                                                    \
+  gb_launch(delta_rule_kernel<P>, grid, 32 * P, 0, stream, q, k, v, ld, beta_logit, a_logit, ldg, A_log, dt_bias, state, cu, \
+            seq_slot, y, H, G, D, V, qscale)
+  switch (lanes_for(D)) {
+    case 1: GB_DELTA(1); break;
+    case 2: GB_DELTA(2); break;
+    case 4: GB_DELTA(4); break;
+    default: GB_DELTA(8);
   }
-  gb_launch(delta_rule_kernel, dim3(nseq, H), threads, smem, stream, q, k, v, ld, beta_logit, a_logit, ldg, A_log, dt_bias,
-            state, cu, seq_slot, y, H, G, D, V, qscale);
+#undef GB_DELTA
   return gb_launch_status();
 }
 
 // ------------------------------------------------------------------ selective state space, scalar decay per head
-// One block per (sequence, head); thread j owns column j of S [N, V].  Per token, with
-// dt = softplus(dt_raw + dt_bias):  S <- exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x.
-__global__ void ssd_scan_kernel(const float* __restrict__ x, const float* __restrict__ Bm, const float* __restrict__ Cm,
-                                long long ld, const float* __restrict__ dt_raw, long long ldd, const float* __restrict__ A_log,
-                                const float* __restrict__ dt_bias, const float* __restrict__ skip, float* __restrict__ state,
-                                const int* __restrict__ cu, const int* __restrict__ seq_slot, float* __restrict__ y, int H,
-                                int G, int N, int V) {
-  extern __shared__ float sm[];
-  float* S = sm;                 // [N][V]
-  float* bc = S + (size_t)N * V; // two buffers of B[N], C[N]
+// The state of a head is S [n_state, vdim]; blocks, columns, lanes and the order in memory as
+// above (n_state <= 32 P).  Per token, with dt = softplus(dt_raw + dt_bias):
+//   S <- exp(-exp(A_log) dt) S + dt B x^T;   y = S^T C + D x.
+template <int P>
+__global__ void __launch_bounds__(32 * P) ssd_scan_kernel(const float* __restrict__ x, const float* __restrict__ Bm,
+                                                         const float* __restrict__ Cm, long long ld,
+                                                         const float* __restrict__ dt_raw, long long ldd,
+                                                         const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                                         const float* __restrict__ skip, float* __restrict__ state,
+                                                         const int* __restrict__ cu, const int* __restrict__ seq_slot,
+                                                         float* __restrict__ y, int H, int G, int N, int V) {
+  __shared__ __align__(16) float bc[2][GROUP][2][padded_size(P)];   // [buffer][token][B | C][state dims, padded]
+  __shared__ float xs[2][GROUP][32], steps[2][GROUP], pre[GROUP][2];
   pdl_release_next();
   pdl_wait_prior();
-  const int b = blockIdx.x, head = blockIdx.y, g = head / (H / G), tid = threadIdx.x, nthr = blockDim.x;
+  const int b = blockIdx.x, head = blockIdx.y, g = head / (H / G), tid = threadIdx.x;
+  const int col = blockIdx.z * 32 + tid / P, part = tid % P;
+  const bool live = col < V;
   const int t0 = cu[b], t1 = cu[b + 1];
-  float* Sg = state + ((size_t)seq_slot[b] * H + head) * N * V;
-  for (int i = tid; i < N * V; i += nthr) S[i] = Sg[i];
-  const float rate = expf(A_log[head]), dtb = dt_bias[head], dskip = skip[head];
-  float x_next = 0.f, dt_next = 0.f;
-  if (t0 < t1) {
-    for (int i = tid; i < N; i += nthr) {
-      bc[i] = Bm[(size_t)t0 * ld + g * N + i];
-      bc[N + i] = Cm[(size_t)t0 * ld + g * N + i];
-    }
-    if (tid < V) x_next = x[(size_t)t0 * ld + head * V + tid];
-    dt_next = dt_raw[(size_t)t0 * ldd + head];
+  float4* Sg = (float4*)(state + ((size_t)seq_slot[b] * H + head) * 8 * V * P * 4);
+  float S[SLICE];
+#pragma unroll
+  for (int r = 0; r < SLICE / 4; ++r) {
+    const float4 s4 = live ? Sg[((size_t)r * V + col) * P + part] : make_float4(0.f, 0.f, 0.f, 0.f);
+    S[4 * r] = s4.x; S[4 * r + 1] = s4.y; S[4 * r + 2] = s4.z; S[4 * r + 3] = s4.w;
   }
-  __syncthreads();
-  for (int t = t0; t < t1; ++t) {
-    const int buf = (t - t0) & 1;
-    const float* Bs = bc + buf * 2 * N;
-    const float* Cs = Bs + N;
-    const float xv = x_next, dt = softplus_f(dt_next + dtb);
-    float pb[PREFETCH], pc[PREFETCH];
-    if (t + 1 < t1) {
-#pragma unroll
-      for (int r = 0; r < PREFETCH; ++r) {
-        const int i = tid + r * nthr;
-        if (i < N) {
-          pb[r] = Bm[(size_t)(t + 1) * ld + g * N + i];
-          pc[r] = Cm[(size_t)(t + 1) * ld + g * N + i];
-        }
+  const float rate = expf(A_log[head]), dtb = dt_bias[head], dskip = skip[head];
+  if (tid >= N)
+    for (int j = 0; j < 2 * GROUP; ++j) bc[j / GROUP][j % GROUP][0][padded(tid)] = bc[j / GROUP][j % GROUP][1][padded(tid)] = 0.f;
+  auto bring = [&](int first, int buf) {
+    for (int j = 0; j < GROUP && first + j < t1; ++j) {
+      const size_t t = first + j;
+      if (tid < N) {
+        copy_async4(&bc[buf][j][0][padded(tid)], Bm + t * ld + g * N + tid);
+        copy_async4(&bc[buf][j][1][padded(tid)], Cm + t * ld + g * N + tid);
       }
-      if (tid < V) x_next = x[(size_t)(t + 1) * ld + head * V + tid];
-      dt_next = dt_raw[(size_t)(t + 1) * ldd + head];
+      if (live && part == 0) copy_async4(&xs[buf][j][tid / P], x + t * ld + head * V + col);
+      if (tid == 0) copy_async4(&steps[buf][j], dt_raw + t * ldd + head);
     }
-    const float decay = expf(-rate * dt);
-    if (tid < V) {
-      const float dx = dt * xv;
-      float acc = 0.f;
-      for (int n = 0; n < N; ++n) {
-        const float s = fmaf(Bs[n], dx, decay * S[n * V + tid]);
-        S[n * V + tid] = s;
-        acc = fmaf(s, Cs[n], acc);
-      }
-      y[(size_t)t * H * V + head * V + tid] = fmaf(dskip, xv, acc);
+    copy_async_commit();
+  };
+  bring(t0, 0);
+  for (int first = t0; first < t1; first += GROUP) {
+    const int buf = ((first - t0) / GROUP) & 1;
+    if (first + GROUP < t1) {
+      bring(first + GROUP, buf ^ 1);
+      copy_async_wait<1>();
+    } else {
+      copy_async_wait<0>();
     }
-    if (t + 1 < t1) {
-      float* nb = bc + (buf ^ 1) * 2 * N;
+    __syncthreads();
+    const int n = min(GROUP, t1 - first);
+    if (tid < n) {                            // step sizes and decays of the group, a token a thread
+      const float dt = softplus_f(steps[buf][tid] + dtb);
+      pre[tid][0] = dt;
+      pre[tid][1] = expf(-rate * dt);
+    }
+    __syncthreads();
+    for (int j = 0; j < n; ++j) {
+      const float4* Bs = (const float4*)(bc[buf][j][0] + part * (SLICE + 4));
+      const float4* Cs = (const float4*)(bc[buf][j][1] + part * (SLICE + 4));
+      const float xv = live ? xs[buf][j][tid / P] : 0.f;
+      const float decay = pre[j][1], dx = pre[j][0] * xv;
+      float acc = 0.f, acc2 = 0.f;
 #pragma unroll
-      for (int r = 0; r < PREFETCH; ++r) {
-        const int i = tid + r * nthr;
-        if (i < N) { nb[i] = pb[r]; nb[N + i] = pc[r]; }
+      for (int r = 0; r < SLICE / 4; ++r) {
+        const float4 bv = Bs[r], cv = Cs[r];
+        S[4 * r] = fmaf(bv.x, dx, decay * S[4 * r]);         acc = fmaf(S[4 * r], cv.x, acc);
+        S[4 * r + 1] = fmaf(bv.y, dx, decay * S[4 * r + 1]); acc2 = fmaf(S[4 * r + 1], cv.y, acc2);
+        S[4 * r + 2] = fmaf(bv.z, dx, decay * S[4 * r + 2]); acc = fmaf(S[4 * r + 2], cv.z, acc);
+        S[4 * r + 3] = fmaf(bv.w, dx, decay * S[4 * r + 3]); acc2 = fmaf(S[4 * r + 3], cv.w, acc2);
       }
+      acc = lanes_sum<P>(acc + acc2);
+      if (live && part == 0) y[(size_t)(first + j) * H * V + head * V + col] = fmaf(dskip, xv, acc);
     }
     __syncthreads();
   }
-  for (int i = tid; i < N * V; i += nthr) Sg[i] = S[i];
+  if (live) {
+#pragma unroll
+    for (int r = 0; r < SLICE / 4; ++r)
+      Sg[((size_t)r * V + col) * P + part] = make_float4(S[4 * r], S[4 * r + 1], S[4 * r + 2], S[4 * r + 3]);
+  }
 }
 
+// state: [slots, H, gb_state_floats(N, V)] float32.
 GB_EXPORT int gb_ssd_scan(const float* x, const float* Bm, const float* Cm, long long ld, const float* dt_raw, long long ldd,
                           const float* A_log, const float* dt_bias, const float* skip, float* state, const int* cu,
                           const int* seq_slot, float* y, int nseq, int H, int G, int N, int V, cudaStream_t stream) {
   if (nseq <= 0) return 0;
-  int threads = ((V + 31) / 32) * 32;
-  if (G <= 0 || H % G || V <= 0 || threads > 1024 || N <= 0 || N > PREFETCH * threads) return GB_ERR_SIZE;
-  const size_t smem = ((size_t)N * V + 4 * N) * sizeof(float);
-  if (smem > 200 * 1024) return GB_ERR_SIZE;
-  static bool raised = false;
-  if (!raised) {
-    cudaFuncSetAttribute(ssd_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    raised = true;
+  if (G <= 0 || H % G || V <= 0 || N <= 0 || N > 8 * SLICE || ((uintptr_t)state & 15)) return GB_ERR_SIZE;
+  dim3 grid(nseq, H, (V + 31) / 32);
+#define GB_SSD(P)                                                                                                       \
+  gb_launch(ssd_scan_kernel<P>, grid, 32 * P, 0, stream, x, Bm, Cm, ld, dt_raw, ldd, A_log, dt_bias, skip, state, cu, seq_slot, y, \
+            H, G, N, V)
+  switch (lanes_for(N)) {
+    case 1: GB_SSD(1); break;
+    case 2: GB_SSD(2); break;
+    case 4: GB_SSD(4); break;
+    default: GB_SSD(8);
   }
-  gb_launch(ssd_scan_kernel, dim3(nseq, H), threads, smem, stream, x, Bm, Cm, ld, dt_raw, ldd, A_log, dt_bias, skip, state, cu,
-            seq_slot, y, H, G, N, V);
+#undef GB_SSD
   return gb_launch_status();
 }
 

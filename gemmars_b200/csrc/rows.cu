@@ -36,26 +36,79 @@ GB_EXPORT int gb_gather_add(const void* table, int table_dtype, const int* idx, 
   return gb_launch_status();
 }
 
-// x[t, :] += y[t, :] * rstd(y[t]) * w.  One block a row; the row of y is read twice (the second
-// time from L1/L2).  The order of the additions depends on n and the block size alone.
-__global__ void __launch_bounds__(256) rmsnorm_add_kernel(const float* __restrict__ y, const float* __restrict__ w,
-                                                          float* __restrict__ x, int n, float eps) {
+// x[t, :] += y[t, :] * rstd(y[t]) * w, and, when a second weight is given, the norm that reads the
+// stream next in the same pass: h[t, :] = x[t, :] * rstd(x[t]) * w2 (x the row after the add).  One
+// block a row; the row is kept in registers between the passes where it fits (rows up to 8 floats a
+// thread), else read again.  The order of the additions depends on n and the block size alone.
+template <typename O>
+__global__ void __launch_bounds__(512) rmsnorm_add_kernel(const float* __restrict__ y, const float* __restrict__ w,
+                                                          float* __restrict__ x, int n, float eps, const float* __restrict__ w2,
+                                                          O* __restrict__ h, float eps2) {
   __shared__ float scratch[33];
   pdl_release_next();
   pdl_wait_prior();
+  constexpr int KEEP = 8;
   const float* row = y + (size_t)blockIdx.x * n;
   float* out = x + (size_t)blockIdx.x * n;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+  const bool keep = n <= KEEP * (int)blockDim.x;
+  float held[KEEP], ss = 0.f;
+  if (keep) {
+#pragma unroll
+    for (int u = 0; u < KEEP; ++u) {
+      const int i = threadIdx.x + u * blockDim.x;
+      held[u] = i < n ? row[i] : 0.f;
+      ss = fmaf(held[u], held[u], ss);
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+  }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)n + eps);
-  for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] += row[i] * inv * w[i];
+  float ss2 = 0.f;
+  if (keep) {
+#pragma unroll
+    for (int u = 0; u < KEEP; ++u) {
+      const int i = threadIdx.x + u * blockDim.x;
+      if (i < n) {
+        held[u] = out[i] + held[u] * inv * w[i];
+        out[i] = held[u];
+        ss2 = fmaf(held[u], held[u], ss2);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const float v = out[i] + row[i] * inv * w[i];
+      out[i] = v;
+      ss2 = fmaf(v, v, ss2);
+    }
+  }
+  if (!w2) return;
+  ss2 = block_sum(ss2, scratch);
+  const float inv2 = 1.0f / sqrtf(ss2 / (float)n + eps2);
+  O* hrow = h + (size_t)blockIdx.x * n;
+  if (keep) {
+#pragma unroll
+    for (int u = 0; u < KEEP; ++u) {
+      const int i = threadIdx.x + u * blockDim.x;
+      if (i < n) hrow[i] = from_f32<O>(held[u] * inv2 * w2[i]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) hrow[i] = from_f32<O>(out[i] * inv2 * w2[i]);
+  }
 }
 
-GB_EXPORT int gb_rmsnorm_add(const float* y, const float* w, float* x, int rows, int n, float eps, cudaStream_t stream) {
+// w2, h (of h_dtype), eps2: the following norm, or null.
+GB_EXPORT int gb_rmsnorm_add(const float* y, const float* w, float* x, int rows, int n, float eps, const float* w2, void* h,
+                             int h_dtype, float eps2, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (n <= 0) return GB_ERR_SIZE;
-  gb_launch(rmsnorm_add_kernel, rows, n >= 2048 ? 256 : 128, 0, stream, y, w, x, n, eps);
+  const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+  if (w2 && h_dtype == GB_BF16)
+    gb_launch(rmsnorm_add_kernel<bf16>, rows, threads, 0, stream, y, w, x, n, eps, w2, (bf16*)h, eps2);
+  else if (!w2 || h_dtype == GB_F32)
+    gb_launch(rmsnorm_add_kernel<float>, rows, threads, 0, stream, y, w, x, n, eps, w2, (float*)h, eps2);
+  else
+    return GB_ERR_DTYPE;
   return gb_launch_status();
 }
 

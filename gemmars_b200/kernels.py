@@ -1347,16 +1347,25 @@ def gather_add(table: torch.Tensor, idx: torch.Tensor, x: torch.Tensor):
            2 * _nbytes(x) + idx.numel() * table.shape[1] * table.element_size())
 
 
-def rmsnorm_add(y: torch.Tensor, weight: torch.Tensor, x: torch.Tensor, eps: float):
+def rmsnorm_add(y: torch.Tensor, weight: torch.Tensor, x: torch.Tensor, eps: float, then=None):
     """x[t] += y[t] * (mean(y[t]^2) + eps)^-1/2 * weight: a norm on a sublayer's output, added into
-    the float32 residual stream."""
+    the float32 residual stream.  ``then`` = (weight2, eps2, out): the norm that reads the stream
+    next, taken in the same pass: out[t] = x[t] * (mean(x[t]^2) + eps2)^-1/2 * weight2."""
     _cuda(y, weight, x)
     assert y.dtype == torch.float32 and x.dtype == torch.float32 and weight.dtype == torch.float32
     assert y.is_contiguous() and x.is_contiguous() and y.shape == x.shape and weight.numel() == x.shape[-1]
     n = x.shape[-1]
-    f = _fn("rows", "gb_rmsnorm_add", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p])
-    _check(f(y.data_ptr(), weight.data_ptr(), x.data_ptr(), x.numel() // n, n, eps, _stream()), "rmsnorm_add", "norm",
-           _nbytes(y, weight) + 2 * _nbytes(x))
+    w2 = out = None
+    eps2 = 0.0
+    if then is not None:
+        w2, eps2, out = then
+        _cuda(w2, out)
+        assert w2.dtype == torch.float32 and w2.numel() == n and out.is_contiguous() and out.shape == x.shape
+    f = _fn("rows", "gb_rmsnorm_add",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_float, c_void_p])
+    _check(f(y.data_ptr(), weight.data_ptr(), x.data_ptr(), x.numel() // n, n, eps, _ptr(w2), _ptr(out),
+             dtype_code(out.dtype) if out is not None else F32, eps2, _stream()), "rmsnorm_add", "norm",
+           _nbytes(y, weight, out) + 2 * _nbytes(x))
 
 
 def gated_act(gu: torch.Tensor, out: torch.Tensor, act: str = "silu"):
@@ -1421,12 +1430,28 @@ def short_filter_state(u, state, cu_seqlens, seq_slot, k: int):
              c, k, _stream()), "short_filter_state", "elementwise", 0)
 
 
+def recurrent_state_floats(dims: int, vdim: int) -> int:
+    """Floats that ``delta_rule`` and ``ssd_scan`` keep per head for a state matrix [dims, vdim]: the
+    dims are padded to 32 lanes' worth (32, 64, 128 or 256) and stored in the order the kernel's
+    lanes read them (see csrc/recurrent.cu)."""
+    lanes = 1 if dims <= 32 else (2 if dims <= 64 else (4 if dims <= 128 else 8))
+    return 32 * lanes * vdim
+
+
+def recurrent_state_matrix(head_state: torch.Tensor, dims: int, vdim: int) -> torch.Tensor:
+    """The state matrix [dims, vdim] that one head's stored floats hold: element (d, col) with
+    d = 32 part + 4 r + e lies at ((r * vdim + col) * lanes + part) * 4 + e."""
+    lanes = head_state.numel() // (32 * vdim)
+    return head_state.reshape(8, vdim, lanes, 4).permute(2, 0, 3, 1).reshape(32 * lanes, vdim)[:dims]
+
+
 def delta_rule(q, k, v, beta_logit, a_logit, a_log, dt_bias, state, cu_seqlens, seq_slot, y, heads, groups, dim, vdim,
                q_scale):
     """The gated delta rule over each sequence of the packed step (float32 throughout):
     S <- g S; u = beta (v - S^T k^); S <- S + k^ u^T; y = S^T q^, with k^, q^ the unit vectors of k
     and q (q^ times ``q_scale``), beta = sigmoid(beta_logit), g = exp(-exp(a_log) softplus(a_logit +
-    dt_bias)).  q, k, v: slices of columns of one [T, *] tensor; ``state`` [slots + 1, heads, dim, vdim]."""
+    dt_bias)).  q, k, v: slices of columns of one [T, *] tensor; ``state`` [slots + 1, heads,
+    recurrent_state_floats(dim, vdim)] (see recurrent_state_matrix); dim up to 256."""
     _cuda(q, k, v, beta_logit, a_logit, a_log, dt_bias, state, cu_seqlens, seq_slot, y)
     for t in (q, k, v, beta_logit, a_logit, y, state):
         assert t.dtype == torch.float32
@@ -1436,7 +1461,7 @@ def delta_rule(q, k, v, beta_logit, a_logit, a_log, dt_bias, state, cu_seqlens, 
     bp, ldg = _cols(beta_logit)
     ap, lda = _cols(a_logit)
     assert ld == ldk == ldv and ldg == lda and y.is_contiguous() and y.shape[1] == heads * vdim
-    assert state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim)
+    assert state.is_contiguous() and tuple(state.shape[1:]) == (heads, recurrent_state_floats(dim, vdim))
     f = _fn("recurrent", "gb_delta_rule",
             [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
@@ -1448,7 +1473,8 @@ def delta_rule(q, k, v, beta_logit, a_logit, a_log, dt_bias, state, cu_seqlens, 
 def ssd_scan(x, b, c, dt_raw, a_log, dt_bias, skip, state, cu_seqlens, seq_slot, y, heads, groups, n_state, vdim):
     """The state-space recurrence with one decay per head over each sequence of the packed step
     (float32): dt = softplus(dt_raw + dt_bias); S <- exp(-exp(a_log) dt) S + dt B x^T; y = S^T C +
-    skip x.  x, b, c: slices of columns of one tensor; ``state`` [slots + 1, heads, n_state, vdim]."""
+    skip x.  x, b, c: slices of columns of one tensor; ``state`` [slots + 1, heads,
+    recurrent_state_floats(n_state, vdim)]; n_state up to 256."""
     _cuda(x, b, c, dt_raw, a_log, dt_bias, skip, state, cu_seqlens, seq_slot, y)
     for t in (x, b, c, dt_raw, y, state):
         assert t.dtype == torch.float32
@@ -1457,7 +1483,7 @@ def ssd_scan(x, b, c, dt_raw, a_log, dt_bias, skip, state, cu_seqlens, seq_slot,
     cp, ldc = _cols(c)
     dp, ldd = _cols(dt_raw)
     assert ld == ldb == ldc and y.is_contiguous() and y.shape[1] == heads * vdim
-    assert state.is_contiguous() and tuple(state.shape[1:]) == (heads, n_state, vdim)
+    assert state.is_contiguous() and tuple(state.shape[1:]) == (heads, recurrent_state_floats(n_state, vdim))
     f = _fn("recurrent", "gb_ssd_scan",
             [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
@@ -1549,10 +1575,11 @@ def attention_capped(ctx, q, out, heads, kcache, vcache, page_table, page_size, 
         f = _fn("attention_capped_mma", "gb_attention_capped_mma",
                 [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_longlong, c_float,
-                 c_void_p], (("GB_HEAD_DIM", dim), ("GB_VALUE_DIM", vdim)))
+                 c_int, c_void_p], (("GB_HEAD_DIM", dim), ("GB_VALUE_DIM", vdim)))
         _check(f(qp, ldq, op, ldo, kcache.data_ptr(), vcache.data_ptr(), page_table.data_ptr(), page_table.shape[1], page_size,
                  groups, dim, vdim, ctx.cu_seqlens.data_ptr(), ctx.seq_start.data_ptr(), ctx.seq_slot.data_ptr(), ctx.n_seqs,
-                 q.shape[0], heads, int(window or 0), scale, float(cap or 0.0), gp, ldg, out_scale, _stream()),
+                 q.shape[0], heads, int(window or 0), scale, float(cap or 0.0), gp, ldg, out_scale,
+                 1 if q.shape[0] == ctx.n_seqs else 0, _stream()),
                "attention_capped_mma", "attention", 2 * q.numel() * q.element_size())
         return
     f = _fn("attention_capped", "gb_attention_capped",

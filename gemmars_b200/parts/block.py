@@ -104,11 +104,17 @@ class SandwichBlock(Block):
         mine = self.split_caches(caches)
         y = torch.zeros_like(x)
         self.mixer.forward(ctx, self.mixer_norm.forward(ctx, x), y, mine["mixer"], writes_cache)
-        self.mixer_post_norm.add_normed(ctx, y, x)
-        if self.ffn is not None:
-            y.zero_()
-            self.ffn.forward(ctx, self.ffn_norm.forward(ctx, x), y)
-            self.ffn_post_norm.add_normed(ctx, y, x)
+        if self.ffn is None:
+            self.mixer_post_norm.add_normed(ctx, y, x)
+            return
+        # the norm after the mixer and the norm before the feed-forward read the same rows: one pass
+        fused = isinstance(self.ffn_norm, type(self.mixer_post_norm)) and hasattr(self.ffn_norm, "weight")
+        h = self.mixer_post_norm.add_normed(ctx, y, x, self.ffn_norm if fused else None)
+        if h is None:
+            h = self.ffn_norm.forward(ctx, x)
+        y.zero_()
+        self.ffn.forward(ctx, h, y)
+        self.ffn_post_norm.add_normed(ctx, y, x)
 
 
 def _plain(h):

@@ -40,6 +40,8 @@ class GatedDeltaRule(Part):
             raise ValueError(f"gated_delta: {self.heads} heads are not a multiple of {self.kv_heads} q/k heads")
         if not 1 <= self.taps <= 8:
             raise ValueError(f"gated_delta: a filter of {self.taps} taps is not supported (1 to 8)")
+        if self.dim > 256:
+            raise ValueError(f"gated_delta: q/k heads of {self.dim} are wider than the kernel takes (256)")
         self.qk, self.hv = self.kv_heads * self.dim, self.heads * self.vdim
         self.channels = 2 * self.qk + self.hv            # what the filter runs over: q | k | v
         self.proj = self.o = self.filter = self.a_log = self.dt_bias = self.norm = None
@@ -63,7 +65,7 @@ class GatedDeltaRule(Part):
         return kernels.gemm_units(self.compute) + [("recurrent", ())]
 
     def cache_needs(self):
-        return [StateNeed((self.taps - 1, self.channels)), StateNeed((self.heads, self.dim, self.vdim))]
+        return [StateNeed((self.taps - 1, self.channels)), StateNeed((self.heads, kernels.recurrent_state_floats(self.dim, self.vdim)))]
 
     def weight_bytes(self):
         small = sum(4 * t.numel() for t in (self.filter, self.a_log, self.dt_bias, self.norm) if t is not None)

@@ -47,9 +47,15 @@ class RMSNorm(Part):
         kernels.rmsnorm(x, self.weight, out, self.eps, rows_index)
         return out
 
-    def add_normed(self, ctx, y, x):
-        """x += norm(y): ``y`` a sublayer's float32 output, ``x`` the residual stream."""
-        kernels.rmsnorm_add(y, self.weight, x, self.eps)
+    def add_normed(self, ctx, y, x, then=None):
+        """x += norm(y): ``y`` a sublayer's float32 output, ``x`` the residual stream.  ``then``: an
+        RMSNorm part that reads the stream next; its output is made in the same pass and returned."""
+        if then is None:
+            kernels.rmsnorm_add(y, self.weight, x, self.eps)
+            return None
+        out = torch.empty(x.shape, dtype=then.act_dtype, device=x.device)
+        kernels.rmsnorm_add(y, self.weight, x, self.eps, (then.weight, then.eps, out))
+        return out
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -41,6 +41,8 @@ class StateSpaceDual(Part):
             raise ValueError(f"ssd: {self.inner} channels cannot be normed in {self.norm_groups} equal parts")
         if not 1 <= self.taps <= 8:
             raise ValueError(f"ssd: a filter of {self.taps} taps is not supported (1 to 8)")
+        if self.n_state > 256:
+            raise ValueError(f"ssd: a state of {self.n_state} is larger than the kernel takes (256)")
         self.channels = self.inner + 2 * self.groups * self.n_state     # what the filter runs over: x | B | C
         self.proj = self.o = self.filter = self.filter_bias = self.a_log = self.dt_bias = self.skip = self.norm = None
 
@@ -61,7 +63,7 @@ class StateSpaceDual(Part):
         return kernels.gemm_units(self.compute) + [("recurrent", ())]
 
     def cache_needs(self):
-        return [StateNeed((self.taps - 1, self.channels)), StateNeed((self.heads, self.n_state, self.vdim))]
+        return [StateNeed((self.taps - 1, self.channels)), StateNeed((self.heads, kernels.recurrent_state_floats(self.n_state, self.vdim)))]
 
     def weight_bytes(self):
         small = sum(4 * t.numel() for t in (self.filter, self.filter_bias, self.a_log, self.dt_bias, self.skip, self.norm)

@@ -71,6 +71,46 @@ for _name, (_t, _q) in PAIRS.items():
     PAIR_SHAPES[f"beside-{_name}"] = (f"Qwen3 shape beside Toretar '{_name}'", _q)
 
 
+def kuporax_shape(width, ff, heads, window, order=("delta", "parallel", "parallel", "delta"), vocab=102400, positions=16384):
+    """A Kuporax config.json object with ``heads`` heads of 128 in every mixer: delta layers with
+    half as many q/k heads as heads; side-by-side layers of windowed attention (keys and values of
+    128, a quarter as many kv heads) and a state-space branch with twice as many heads of 64 and a
+    state of 128."""
+    delta = {"type": "delta", "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "conv": 4},
+             "mlp": {"kind": "dense", "ff": ff}}
+    parallel = {"type": "parallel",
+                "mixer": {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "conv": 3,
+                                   "scale": 128 ** -0.5, "softcap": 30.0, "mask": {"size": window},
+                                   "rot": {"base": 1000000.0, "dims": 128}},
+                          "right": {"heads": 2 * heads, "vdim": 64, "state": 128, "groups": max(1, heads // 4),
+                                    "norm_groups": max(1, heads // 4), "conv": 4},
+                          "left_scale": 1.0, "right_scale": 1.0},
+                "mlp": {"kind": "dense", "ff": ff}}
+    return {"architecture": "Kuporax", "vocab": vocab, "width": width, "max_positions": positions, "logit_scale": 1.0,
+            "norm": {"eps": 1e-6}, "layers": [delta if kind == "delta" else parallel for kind in order]}
+
+
+def _kuporax_pair(width, ff, heads, window):
+    """A Kuporax shape and the Qwen3 shape beside it: the same width, depth, vocabulary and
+    feed-forward, heads of 128 with a quarter as many kv heads, and the same window on every layer."""
+    k = kuporax_shape(width, ff, heads, window)
+    q = qwen3_shape(len(k["layers"]), width, heads, max(1, heads // 4), ff, False)
+    q.update({"vocab_size": k["vocab"], "use_sliding_window": True, "sliding_window": window,
+              "layer_types": ["sliding_attention"] * len(k["layers"])})
+    return k, q
+
+
+# Layer sizes in the range of released models that mix recurrent layers with windowed attention, four layers each
+KUPORAX_PAIRS = {
+    "small": _kuporax_pair(1024, 4096, 8, 512),
+    "lite": _kuporax_pair(2048, 8192, 16, 1024),
+    "mid": _kuporax_pair(4096, 12288, 32, 2048),
+}
+for _name, (_k, _q) in KUPORAX_PAIRS.items():
+    PAIR_SHAPES[f"kuporax-{_name}"] = (f"Kuporax shape '{_name}'", _k)
+    PAIR_SHAPES[f"beside-kuporax-{_name}"] = (f"Qwen3 shape beside Kuporax '{_name}'", _q)
+
+
 def random_engine(cfg, max_batch, cache_tokens, options=""):
     """An engine over random weights of ``cfg`` made on the device; the tensors are taken out of
     their dict as they are bound, so that a model of 65 GB and its stacked q/k/v and gate/up copies

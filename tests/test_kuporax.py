@@ -48,12 +48,13 @@ def test_what_the_layers_keep_per_sequence():
     model = build_model(raw_config=KUPORAX_A, tensors=random_weights(KUPORAX_A, 1), dtype="float32", device="cpu",
                         compile_kernels=False)
     needs = dict(model.cache_needs())
+    # (a recurrent state's dims are padded to 32 a lane: 32 * lanes * vdim floats a head)
     # side by side: keys of 24 with values of 40 in a window of 50 and one tap of memory, then the
     # state-space branch's filter memory and state
-    assert needs[0] == [KVNeed(2, 24, 50, 40), StateNeed((1, 6 * 24 + 2 * 40)), StateNeed((2, 48 + 24)), StateNeed((3, 12, 16))]
-    assert needs[1] == [StateNeed((2, 2 * 64 + 96)), StateNeed((4, 16, 24))]
+    assert needs[0] == [KVNeed(2, 24, 50, 40), StateNeed((1, 6 * 24 + 2 * 40)), StateNeed((2, 48 + 24)), StateNeed((3, 32 * 16))]
+    assert needs[1] == [StateNeed((2, 2 * 64 + 96)), StateNeed((4, 32 * 24))]
     # a filter of one tap remembers nothing
-    assert needs[2] == [KVNeed(3, 32, 9, 16), StateNeed((1, 32 + 2 * 4 * 20)), StateNeed((4, 20, 8))]
+    assert needs[2] == [KVNeed(3, 32, 9, 16), StateNeed((1, 32 + 2 * 4 * 20)), StateNeed((4, 32 * 8))]
     cache = SequenceCache(model.cache_needs(), 512, 4, 600, 64, torch.float32, "cpu")
     slot = cache.open()
     cache.extend(slot, 300)

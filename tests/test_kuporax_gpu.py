@@ -70,7 +70,16 @@ def test_row_kernels():
         r, rn = _rand(rng, (5, n))
         w, wn = _rand(rng, (n,))
         kernels.rmsnorm_add(y, w, r, 1e-5)
-        assert np.abs(r.double().cpu().numpy() - (rn + plain.rms_scale(yn, 1e-5) * wn)).max() < 2e-5
+        want = rn + plain.rms_scale(yn, 1e-5) * wn
+        assert np.abs(r.double().cpu().numpy() - want).max() < 2e-5
+        # with the norm that reads the stream next taken in the same pass
+        w2, w2n = _rand(rng, (n,))
+        for dtype in ("float32", "bfloat16"):
+            r2 = torch.from_numpy(rn).float().to(DEV)
+            h = torch.empty((5, n), dtype=_dt(dtype), device=DEV)
+            kernels.rmsnorm_add(y, w, r2, 1e-5, (w2, 1e-6, h))
+            assert torch.equal(r2, r)
+            assert np.abs(h.double().cpu().numpy() - plain.rms_scale(want, 1e-6) * w2n).max() < (2e-5 if dtype == "float32" else 4e-2)
     for dtype in ("float32", "bfloat16"):
         gu, gn = _rand(rng, (11, 2 * 36), _dt(dtype), scale=2.0)
         out = torch.empty((11, 36), dtype=_dt(dtype), device=DEV)
@@ -124,7 +133,7 @@ def test_short_filter_carries_its_last_inputs(taps, bias, act, dtype):
             state[s].zero_()                          # what opening a sequence does
 
 
-@pytest.mark.parametrize("heads,groups,dim,vdim", [(4, 4, 16, 24), (6, 2, 8, 40), (3, 1, 64, 64), (2, 2, 128, 128), (1, 1, 20, 7)])
+@pytest.mark.parametrize("heads,groups,dim,vdim", [(4, 4, 16, 24), (6, 2, 8, 40), (3, 1, 64, 64), (2, 2, 128, 128), (1, 1, 20, 7), (2, 1, 200, 72)])
 def test_delta_rule_alone(heads, groups, dim, vdim):
     """Whole sequences against portions of 1, 2, 5 and 33 tokens, in slots out of order; the unit
     norms, the decay and beta are the kernel's work.  One k of a sequence is made large and its v
@@ -154,7 +163,7 @@ def test_delta_rule_alone(heads, groups, dim, vdim):
         want.append(plain.delta_scan(q, k, v, beta, decay))
     qk = groups * dim
     for sizes in ([1000], [1, 2, 5, 33], [1]):
-        state = torch.zeros((5, heads, dim, vdim), dtype=torch.float32, device=DEV)
+        state = torch.zeros((5, heads, kernels.recurrent_state_floats(dim, vdim)), dtype=torch.float32, device=DEV)
         got = [np.zeros((n, heads * vdim)) for n in lens]
         cuts = [_cuts(n, sizes) for n in lens]
         for step in range(max(len(c) for c in cuts)):
@@ -172,7 +181,8 @@ def test_delta_rule_alone(heads, groups, dim, vdim):
                 at += hi - lo
         for i, (out, final) in enumerate(want):
             assert np.abs(got[i] - out.reshape(lens[i], -1)).max() < 2e-5 * max(1.0, np.abs(out).max())
-            assert np.abs(state[slots[i]].double().cpu().numpy() - final).max() < 2e-5 * max(1.0, np.abs(final).max())
+            held = torch.stack([kernels.recurrent_state_matrix(state[slots[i], h], dim, vdim) for h in range(heads)])
+            assert np.abs(held.double().cpu().numpy() - final).max() < 2e-5 * max(1.0, np.abs(final).max())
         assert not state[2].any() and not state[4].any()
 
 
@@ -194,7 +204,7 @@ def test_state_space_scan_alone(heads, groups, n_state, vdim):
         want.append(plain.ssd_scan(xn[:, :inner].reshape(n, heads, vdim), xn[:, inner:inner + gn_].reshape(n, groups, n_state),
                                    xn[:, inner + gn_:inner + 2 * gn_].reshape(n, groups, n_state), dt, np.exp(an), sn))
     for sizes in ([1000], [2, 1, 9], [1]):
-        state = torch.zeros((4, heads, n_state, vdim), dtype=torch.float32, device=DEV)
+        state = torch.zeros((4, heads, kernels.recurrent_state_floats(n_state, vdim)), dtype=torch.float32, device=DEV)
         got = [np.zeros((n, inner)) for n in lens]
         cuts = [_cuts(n, sizes) for n in lens]
         for step in range(max(len(c) for c in cuts)):
@@ -212,7 +222,8 @@ def test_state_space_scan_alone(heads, groups, n_state, vdim):
                 at += hi - lo
         for i, (out, final) in enumerate(want):
             assert np.abs(got[i] - out.reshape(lens[i], -1)).max() < 2e-5 * max(1.0, np.abs(out).max())
-            assert np.abs(state[slots[i]].double().cpu().numpy() - final).max() < 2e-5 * max(1.0, np.abs(final).max())
+            held = torch.stack([kernels.recurrent_state_matrix(state[slots[i], h], n_state, vdim) for h in range(heads)])
+            assert np.abs(held.double().cpu().numpy() - final).max() < 2e-5 * max(1.0, np.abs(final).max())
         assert not state[3].any()
 
 
