@@ -90,7 +90,20 @@ __device__ int g_status;   // first failure of any launch; 0 when all waits comp
 // result is rounded to bfloat16, whose step is a thousand times their error, and the four epilogue
 // warps have nothing to hide a longer chain behind (measured: the exact expf and division made
 // the gated tile's epilogue 11.5 us per 128 tokens).  For g below -88 the quotient is 0, the limit.
+// A build with -DGB_GATED_ACT=1 gates with the tanh form of GELU instead,
+// 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u, with the hardware's tanh (one instruction).
+#ifndef GB_GATED_ACT
+#define GB_GATED_ACT 0
+#endif
+#if GB_GATED_ACT == 1
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * fmaf(0.044715f * g * g, g, g)));
+  return 0.5f * g * (1.0f + t) * u;
+}
+#else
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+#endif
 
 template <int MODE>
 __device__ __forceinline__ void emit(void* y, size_t idx, float v) {

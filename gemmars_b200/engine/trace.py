@@ -39,11 +39,8 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines=None
     torch.backends.cudnn.allow_tf32 = False
     os.makedirs(out_dir, exist_ok=True)
     model = build_model(model_dir, dtype=dtype, device=device)
-    # ``max_tokens`` counts tokens; a request's last page is rarely full, so every request that may
-    # be live gets a page of slack (a request holds at least one token)
-    slack = min(max_tokens, 256)
-    pages = max(1, -(-max_tokens // PAGE_SIZE)) + slack
-    runner = Runner(model, max_tokens=pages * PAGE_SIZE, max_batch=min(pages, 4096))
+    pages = max(1, -(-max_tokens // PAGE_SIZE))
+    runner = Runner(model, max_tokens=max_tokens, max_batch=min(pages, 4096))
     slots = {}
     for line in lines:
         line = line.strip()

@@ -356,8 +356,12 @@ def norm_link_usable(x, w, m: int, accumulate_splits: Optional[int] = None) -> b
     return ok and (accumulate_splits is None or accumulate_splits >= 2)
 
 
+#: the builds of the product unit whose gated epilogue applies another activation than SiLU
+GATED_ACT_DEFINES = {"silu": (), "gelu_tanh": (("GB_GATED_ACT", 1),)}
+
+
 def gemm_tc(x, w, out, bias=None, accumulate=False, bn=None, splits=None, stages=4, swiglu=False, link_in=None,
-            link_out=None):
+            link_out=None, act="silu"):
     """out = x @ w.T (+ bias) (bfloat16 or float32 out) or out += ... (float32 out), bfloat16
     operands, on the tcgen05 tensor cores.  With ``swiglu``, w stacks a gate matrix over an up
     matrix ([2N, K]) and out[M, N] = silu(x @ gate.T) * (x @ up.T) in bfloat16.
@@ -387,7 +391,7 @@ def gemm_tc(x, w, out, bias=None, accumulate=False, bn=None, splits=None, stages
     if link_in is None and link_out is None:
         f = _fn("gemm_tc", "gb_gemm_tc",
                 [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
-                 c_int, c_int, c_void_p])
+                 c_int, c_int, c_void_p], GATED_ACT_DEFINES[act] if swiglu else ())
         _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, m, n, k, x.stride(0), out.stride(0),
                  bn or auto_bn, splits or auto_splits, stages, _stream()), "gemm_tc", "matmul",
                _nbytes(x, w, bias, out) + (_nbytes(out) if accumulate else 0))
@@ -422,7 +426,8 @@ _part_flags = {}
 PERSISTENT_SPLIT_LAST_ROUND = True
 
 
-def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=None, ctas=None, split_last=None):
+def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=None, ctas=None, split_last=None,
+                       act="silu"):
     """The tensor-core product for prompts (more than 64 rows of x): one CTA per SM walks the output
     tiles, and the epilogue of a tile runs while the next tile's MMAs fill the other accumulator
     buffer.  Operands and modes as gemm_tc.  Where the last round of tiles would leave SMs idle, a
@@ -464,7 +469,7 @@ def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=
             flags = _part_flags[x.device.index] = torch.zeros(max(4 * ctas, 1024), dtype=torch.int32, device=x.device)
     f = _fn("gemm_tc", "gb_gemm_tc_persistent",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
-             c_int, c_void_p, c_void_p])
+             c_int, c_void_p, c_void_p], GATED_ACT_DEFINES[act] if swiglu else ())
     _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, m, n, k, x.stride(0), out.stride(0), bn,
              ctas, _ptr(flags), _stream()), "gemm_tc_persistent", "matmul",
            _nbytes(x, w, bias, out) + (_nbytes(out) if accumulate else 0))
@@ -613,16 +618,33 @@ def gemm_swiglu(x, w_gate_up, out):
 
 
 def gemm_gated(x, w_gate_up, out, act: str = "silu"):
-    """out = act(x @ gate.T) * (x @ up.T) for the stacked [gate; up]: the fused kernel for SiLU,
-    the product followed by ``gated_act`` for the other activations."""
+    """out = act(x @ gate.T) * (x @ up.T) for the stacked [gate; up], act one of GATED_ACTS: in
+    bfloat16 one tensor-core kernel with the activation in its epilogue (a build of the product unit
+    per activation); else the product followed by ``gated_act``."""
     if act == "silu":
         gemm_swiglu(x, w_gate_up, out)
         return
     if isinstance(x, UnscaledRows):
         x = x.materialize()
+    if x.dtype == torch.bfloat16 and gemm_tc_usable(x, w_gate_up) and act in GATED_ACT_DEFINES:
+        if x.shape[0] > GATED_TILE_128_MAX_TOKENS:
+            gemm_tc_persistent(x, w_gate_up, out, swiglu=True, act=act)
+        elif x.shape[0] > 64:
+            gemm_tc(x, w_gate_up, out, swiglu=True, bn=128, splits=1, act=act)
+        else:
+            gemm_tc(x, w_gate_up, out, swiglu=True, act=act)
+        return
     gu = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=x.dtype, device=x.device)
     gemm(x, w_gate_up, gu)
     gated_act(gu, out, act)
+
+
+def gated_units(compute: str, act: str):
+    """The units ``gemm_gated`` may launch."""
+    units = gemm_units(compute) + [("rows", ())]
+    if compute == "bfloat16" and GATED_ACT_DEFINES.get(act):
+        units.append(("gemm_tc", GATED_ACT_DEFINES[act]))
+    return units
 
 
 _STATUS_ENTRIES = ("gb_gemm_tc_status", "gb_attention_prefill_tc_status", "gb_attention_decode_stream_status")

@@ -32,7 +32,9 @@ class GatedMLP(Part):
         self.down = Linear(tensors["down"])
 
     def kernel_units(self):
-        return kernels.gemm_units(self.compute) + [("elementwise", ()), ("rows", ())]
+        if self.activation == "silu":
+            return kernels.gemm_units(self.compute) + [("elementwise", ())]
+        return kernels.gated_units(self.compute, self.activation)
 
     #: forward takes ``then_norm`` and may be given kernels.UnscaledRows for ``h``
     links_norms = True

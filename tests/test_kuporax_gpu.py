@@ -79,16 +79,32 @@ def test_row_kernels():
             h = torch.empty((5, n), dtype=_dt(dtype), device=DEV)
             kernels.rmsnorm_add(y, w, r2, 1e-5, (w2, 1e-6, h))
             assert torch.equal(r2, r)
-            assert np.abs(h.double().cpu().numpy() - plain.rms_scale(want, 1e-6) * w2n).max() < (2e-5 if dtype == "float32" else 4e-2)
+            assert np.abs(h.double().cpu().numpy() - plain.rms_scale(want, 1e-6) * w2n).max() < (2e-5 if dtype == "float32" else 8e-2)
     for dtype in ("float32", "bfloat16"):
         gu, gn = _rand(rng, (11, 2 * 36), _dt(dtype), scale=2.0)
         out = torch.empty((11, 36), dtype=_dt(dtype), device=DEV)
         kernels.gated_act(gu, out, "gelu_tanh")
         want = plain.gelu_tanh(gn[:, :36]) * gn[:, 36:]
-        assert np.abs(out.double().cpu().numpy() - want).max() < (1e-5 if dtype == "float32" else 4e-2)
+        assert np.abs(out.double().cpu().numpy() - want).max() < (1e-5 if dtype == "float32" else 1e-2) * max(1.0, np.abs(want).max())
     z, zn = _rand(rng, (3, 97))
     kernels.scale_rows(z, 1.7)
     assert np.allclose(z.cpu().numpy(), (zn * np.float32(1.7)).astype(np.float32), rtol=1e-6)
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 40, 100, 300])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_gated_product_with_gelu(tokens, dtype):
+    """act(x gate^T) * (x up^T): in bfloat16 the activation rides on the tensor-core product's epilogue."""
+    from gemmars_b200 import kernels
+    rng = np.random.default_rng(tokens)
+    x, xn = _rand(rng, (tokens, 128), _dt(dtype))
+    w, wn = _rand(rng, (2 * 200, 128), _dt(dtype), scale=0.2)
+    out = torch.empty((tokens, 200), dtype=_dt(dtype), device=DEV)
+    kernels.gemm_gated(x, w, out, "gelu_tanh")
+    want = plain.gelu_tanh(xn @ wn[:200].T) * (xn @ wn[200:].T)
+    tol = 2e-5 if dtype == "float32" else 2e-2
+    assert np.abs(out.double().cpu().numpy() - want).max() < tol * max(1.0, np.abs(want).max())
+    kernels.check_status()
 
 
 @pytest.mark.parametrize("taps,bias,act", [(1, False, False), (2, True, True), (4, False, True), (5, True, False), (8, True, True)])
