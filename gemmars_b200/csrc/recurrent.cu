@@ -154,7 +154,6 @@ __global__ void __launch_bounds__(32 * P) delta_rule_kernel(const float* __restr
   __shared__ float vs[2][GROUP][32], gates[2][GROUP][2];
   __shared__ float pre[GROUP][4];                       // per token: decay, 1/|k|, beta, (k^ . q^); then decay * qscale/|q|
   __shared__ float pre_q[GROUP];
-  pdl_release_next();
   pdl_wait_prior();
   const int b = blockIdx.x, head = blockIdx.y, g = head / (H / G), tid = threadIdx.x;
   const int col = blockIdx.z * 32 + tid / P, part = tid % P, lane = tid & 31, warp = tid >> 5;
@@ -238,6 +237,9 @@ __global__ void __launch_bounds__(32 * P) delta_rule_kernel(const float* __restr
     }
     __syncthreads();   // the group after next is brought into this buffer; pre is written again
   }
+  // only now may the kernel after this one start: its waiting blocks would take the room of this
+  // kernel's few warps, which are a chain from token to token
+  pdl_release_next();
   if (live) {
 #pragma unroll
     for (int r = 0; r < SLICE / 4; ++r)
@@ -285,7 +287,6 @@ __global__ void __launch_bounds__(32 * P) ssd_scan_kernel(const float* __restric
                                                          float* __restrict__ y, int H, int G, int N, int V) {
   __shared__ __align__(16) float bc[2][GROUP][2][padded_size(P)];   // [buffer][token][B | C][state dims, padded]
   __shared__ float xs[2][GROUP][32], steps[2][GROUP], pre[GROUP][2];
-  pdl_release_next();
   pdl_wait_prior();
   const int b = blockIdx.x, head = blockIdx.y, g = head / (H / G), tid = threadIdx.x;
   const int col = blockIdx.z * 32 + tid / P, part = tid % P;
@@ -349,6 +350,9 @@ __global__ void __launch_bounds__(32 * P) ssd_scan_kernel(const float* __restric
     }
     __syncthreads();
   }
+  // only now may the kernel after this one start: its waiting blocks would take the room of this
+  // kernel's few warps, which are a chain from token to token
+  pdl_release_next();
   if (live) {
 #pragma unroll
     for (int r = 0; r < SLICE / 4; ++r)
