@@ -27,7 +27,7 @@ def chat_prompt(system, user, think):
 
 
 def parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="gemmars_b200", description="Qwen3 text generation on one B200.")
+    ap = argparse.ArgumentParser(prog="gemmars_b200", description="Text generation on one B200 for the architectures the package knows (Qwen3, Toretar, Kuporax).")
     ap.add_argument("--model", "-m", help="model folder (config.json, model.safetensors)")
     ap.add_argument("--prompt", "-p", help="single prompt (default: read from stdin)")
     ap.add_argument("--chat", action="store_true", help="interactive multi-turn chat")

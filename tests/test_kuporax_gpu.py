@@ -276,7 +276,7 @@ class _Ctx:
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads,groups,dim,vdim,rot,taps,window,cap",
                          [(4, 2, 24, 40, 16, 2, 50, 7.5), (3, 3, 32, 16, 32, 1, 9, 11.0), (8, 2, 64, 128, 32, 4, 130, 30.0),
-                          (2, 1, 48, 80, 0, 3, 64, 0.0), (2, 2, 96, 256, 8, 0, None, 20.0), (5, 1, 16, 300, 16, 2, 200, 3.0)])
+                          (2, 1, 48, 80, 0, 3, 64, 0.0), (2, 2, 80, 256, 8, 0, None, 25.0), (5, 1, 16, 300, 16, 2, 200, 3.0)])
 def test_capped_attention_finds_planted_keys(dtype, heads, groups, dim, vdim, rot, taps, window, cap):
     """One sequence of 300 tokens in shuffled pages beside a short one.  The filter and the rotation
     are checked through the cache rows; then queries are built that point at single keys: far back,

@@ -153,7 +153,7 @@ KUPORAX_B = {
     "architecture": "Kuporax", "vocab": 520, "width": 128, "max_positions": 1024, "logit_scale": 1.0, "norm": {"eps": 1e-6},
     "layers": [
         _kuporax_delta(4, 2, 64, 64, 4, 192),
-        _kuporax_parallel(_kuporax_left(8, 2, 64, 128, 4, 0.125, 30.0, 130, 500000.0, 32), _kuporax_right(4, 32, 64, 2, 2, 4),
+        _kuporax_parallel(_kuporax_left(8, 4, 64, 128, 4, 0.125, 30.0, 130, 250000.0, 32), _kuporax_right(4, 32, 64, 2, 4, 4),
                           0.9, 1.2, 192),
         _kuporax_parallel(_kuporax_left(2, 1, 48, 80, 3, 0.15, 50.0, 64, 1000.0, 0), _kuporax_right(2, 64, 16, 1, 1, 2),
                           1.1, 0.7, 0),
