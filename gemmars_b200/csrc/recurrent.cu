@@ -68,12 +68,54 @@ __global__ void __launch_bounds__(256) short_filter_state_kernel(const T* __rest
     if (i < K - 1) hist[(size_t)i * C + c] = next[i];
 }
 
+// A step of single tokens: the filter and its memory in one kernel, a thread per (sequence,
+// channel), which alone reads and writes that channel's memory.  The sums are taken in the order
+// of the kernel above, so a token gets the same bits whichever kernel ran it.
+template <typename T, typename O>
+__global__ void __launch_bounds__(256) short_filter_single_kernel(const T* __restrict__ u, long long ldu, const float* __restrict__ taps,
+                                                                 const float* __restrict__ bias, float* __restrict__ state,
+                                                                 const int* __restrict__ seq_slot, O* __restrict__ out,
+                                                                 long long ldo, int C, int K, int act) {
+  pdl_release_next();
+  pdl_wait_prior();
+  const int b = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float* hist = state + (size_t)seq_slot[b] * (K - 1) * C;
+  const float now = to_f32(u[(size_t)b * ldu + c]);
+  float acc = bias ? bias[c] : 0.f;
+  float held[MAX_TAPS - 1];
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS - 1; ++j)
+    if (j < K - 1) {
+      held[j] = hist[(size_t)j * C + c];
+      acc = fmaf(taps[(size_t)c * K + j], held[j], acc);
+    }
+  acc = fmaf(taps[(size_t)c * K + K - 1], now, acc);
+  if (act == ACT_SILU) acc = silu_f(acc);
+  out[(size_t)b * ldo + c] = from_f32<O>(acc);
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS - 1; ++j)
+    if (j < K - 1) hist[(size_t)j * C + c] = j + 1 < K - 1 ? held[j + 1] : now;
+}
+
 GB_EXPORT int gb_short_filter(const void* u, int in_dtype, long long ldu, const float* taps, const float* bias, float* state,
                               const int* cu, const int* tok_seq, const int* seq_slot, void* out, int out_dtype, long long ldo,
                               int ntok, int nseq, int C, int K, int act, int update_state, cudaStream_t stream) {
   if (ntok <= 0) return 0;
   if (K < 1 || K > MAX_TAPS || C <= 0) return GB_ERR_SIZE;
   dim3 grid(ntok, (C + 255) / 256), sgrid(nseq, (C + 255) / 256);
+  if (ntok == nseq && update_state && K > 1) {     // every sequence brings one token
+#define GB_SINGLE(T, O)                                                                                                     \
+  gb_launch(short_filter_single_kernel<T, O>, sgrid, 256, 0, stream, (const T*)u, ldu, taps, bias, state, seq_slot, (O*)out, ldo, \
+            C, K, act)
+    if (in_dtype == GB_F32 && out_dtype == GB_F32) GB_SINGLE(float, float);
+    else if (in_dtype == GB_F32 && out_dtype == GB_BF16) GB_SINGLE(float, bf16);
+    else if (in_dtype == GB_BF16 && out_dtype == GB_BF16) GB_SINGLE(bf16, bf16);
+    else if (in_dtype == GB_BF16 && out_dtype == GB_F32) GB_SINGLE(bf16, float);
+    else return GB_ERR_DTYPE;
+#undef GB_SINGLE
+    return gb_launch_status();
+  }
 #define GB_FILTER(T, O)                                                                                                   \
   gb_launch(short_filter_kernel<T, O>, grid, 256, 0, stream, (const T*)u, ldu, taps, bias, (const float*)state, cu, tok_seq, \
             seq_slot, (O*)out, ldo, C, K, act)

@@ -1434,8 +1434,8 @@ def short_filter(u, taps, bias, state, cu_seqlens, tok_seq, seq_slot, out, act: 
              tok_seq.data_ptr(), seq_slot.data_ptr(), op, dtype_code(out.dtype), ldo, u.shape[0], seq_slot.numel(), c, k,
              1 if act else 0, 1 if update_state else 0, _stream()), "short_filter", "elementwise",
            u.numel() * u.element_size() + out.numel() * out.element_size())
-    if update_state and k > 1:
-        count_launches(1)
+    if update_state and k > 1 and u.shape[0] != seq_slot.numel():
+        count_launches(1)      # the kernel that shifts the memory (a step of single tokens does both in one)
 
 
 def short_filter_state(u, state, cu_seqlens, seq_slot, k: int):
