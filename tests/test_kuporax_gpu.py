@@ -570,3 +570,23 @@ def test_greedy_generation_through_the_engine(models):
             total += 1
     assert near >= 0.9 * total
     assert eng16.runner.cache.pages_held() == 0
+
+
+def test_a_conversation_keeps_its_states_between_turns(models):
+    """``Engine.send``: the slot lives on between turns, so the recurrent states, the filters'
+    memories and the window's pages are carried; two turns give what one long sequence gives."""
+    from gemmars_b200 import Engine
+    folder, cfg, w, reqs, _ = models["A"]
+    eng = Engine.load(folder, "dtype=float32;max_batch=2;max_tokens=1024")
+    eng.set("max_tokens", 5)
+    eng.set("stop", "")
+    first, second = reqs[0], reqs[2]
+    a = eng.send(first)
+    want_a, _ = plain.generate(cfg, w, first, 5)
+    assert a.tokens == want_a
+    b = eng.send(second)
+    want_b, _ = plain.generate(cfg, w, list(first) + want_a + list(second), 5)
+    assert b.tokens == want_b
+    eng.reset()
+    assert eng.runner.cache.pages_held() == 0
+    assert eng.send(first).tokens == want_a              # the slot taken again starts from zero states
