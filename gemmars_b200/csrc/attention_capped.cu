@@ -31,6 +31,11 @@ __device__ __forceinline__ float filtered(const T* __restrict__ u, long long ldu
 }
 
 // One block per (token, head): the H query heads, then the G key heads, then the G value heads.
+// A q or k head is filtered into shared memory first, a dim a thread, beside the cosines and sines
+// of the token's angles; then every dim takes its partner from there (with each thread filtering
+// its partner again and taking its own sine and cosine, the kernel was bound by instructions).
+constexpr int MAX_HEAD = 512;
+
 template <typename T>
 __global__ void __launch_bounds__(128) filter_rope_cache_kernel(
     const T* __restrict__ u, long long ldu, const float* __restrict__ taps, const float* __restrict__ state, int K,
@@ -38,6 +43,7 @@ __global__ void __launch_bounds__(128) filter_rope_cache_kernel(
     const int* __restrict__ seq_slot, const int* __restrict__ cu, const int* __restrict__ page_table, int table_width,
     int page_size, T* __restrict__ q_out, long long ldq, T* __restrict__ kcache, T* __restrict__ vcache, int H, int G, int D,
     int Vd) {
+  __shared__ float vals[MAX_HEAD], cs[MAX_HEAD];   // cs: cos[rot / 2], then sin[rot / 2]
   pdl_release_next();
   pdl_wait_prior();
   const int t = blockIdx.x, hh = blockIdx.y, b = tok_seq[t], pos = tok_pos[t], slot = seq_slot[b];
@@ -59,17 +65,18 @@ __global__ void __launch_bounds__(128) filter_rope_cache_kernel(
   if (hh >= H && !kcache) return;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     const int e = hh * D + i;
-    float val = K > 1 ? filtered(u, ldu, row0, local, hist, taps, C, e, K) : to_f32(u[(size_t)t * ldu + e]) * (K == 1 ? taps[e] : 1.f);
+    vals[i] = K > 1 ? filtered(u, ldu, row0, local, hist, taps, C, e, K) : to_f32(u[(size_t)t * ldu + e]) * (K == 1 ? taps[e] : 1.f);
+    if (i < half) sincosf((float)pos * inv_freq[i], &cs[half + i], &cs[i]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float val = vals[i];
     if (i < rot) {
-      const int j = i < half ? i : i - half, partner = i < half ? e + half : e - half;
-      const float other = K > 1 ? filtered(u, ldu, row0, local, hist, taps, C, partner, K)
-                                : to_f32(u[(size_t)t * ldu + partner]) * (K == 1 ? taps[partner] : 1.f);
-      float sn, cs;
-      sincosf((float)pos * inv_freq[j], &sn, &cs);
-      // (a, b) -> (a cos - b sin, b cos + a sin)
-      val = i < half ? val * cs - other * sn : val * cs + other * sn;
+      // the pair (a, b) = (dim j, dim j + half) becomes (a cos - b sin, b cos + a sin)
+      const int j = i < half ? i : i - half;
+      val = i < half ? val * cs[j] - vals[i + half] * cs[half + j] : val * cs[j] + vals[i - half] * cs[half + j];
     }
-    if (hh < H) q_out[(size_t)t * ldq + e] = from_f32<T>(val);
+    if (hh < H) q_out[(size_t)t * ldq + hh * D + i] = from_f32<T>(val);
     else kcache[(((size_t)page * G + (hh - H)) * page_size + off) * D + i] = from_f32<T>(val);
   }
 }
@@ -81,7 +88,8 @@ GB_EXPORT int gb_filter_rope_cache(const void* u, int dtype, long long ldu, cons
                                    long long ldq, void* kcache, void* vcache, int ntok, int H, int G, int D, int Vd,
                                    cudaStream_t stream) {
   if (ntok <= 0) return 0;
-  if (K < 0 || K > MAX_TAPS || rot < 0 || rot > D || rot % 2 || H <= 0 || G <= 0 || D <= 0 || Vd <= 0) return GB_ERR_SIZE;
+  if (K < 0 || K > MAX_TAPS || rot < 0 || rot > D || rot % 2 || H <= 0 || G <= 0 || D <= 0 || D > MAX_HEAD || Vd <= 0)
+    return GB_ERR_SIZE;
   if ((K > 0 && !taps) || (K > 1 && !state) || (rot > 0 && !inv_freq)) return GB_ERR_ARG;
   const dim3 grid(ntok, H + 2 * G);
   if (dtype == GB_F32)

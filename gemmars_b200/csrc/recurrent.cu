@@ -28,23 +28,56 @@ __device__ __forceinline__ float filter_input(const T* __restrict__ u, long long
   return local >= 0 ? to_f32(u[(size_t)(row0 + local) * ldu + c]) : hist[(size_t)(K - 1 + local) * C + c];
 }
 
+// A thread works one channel over `per` consecutive rows of the packed step and keeps the filter's
+// window in registers, so a row costs one load, K multiply-adds and one store (with a thread a row
+// and the window read again for every tap, the kernel was bound by the instructions of its index
+// arithmetic: 231 a row, 0.17 of the memory's rate).  Where the rows pass from one sequence to the
+// next, the window is read anew from the next sequence's memory.  A row's sums are taken in the
+// same order whatever `per` is.
 template <typename T, typename O>
 __global__ void __launch_bounds__(256) short_filter_kernel(const T* __restrict__ u, long long ldu, const float* __restrict__ taps,
                                                           const float* __restrict__ bias, const float* __restrict__ state,
                                                           const int* __restrict__ cu, const int* __restrict__ tok_seq,
                                                           const int* __restrict__ seq_slot, O* __restrict__ out, long long ldo,
-                                                          int C, int K, int act) {
+                                                          int ntok, int per, int C, int K, int act) {
   pdl_release_next();
   pdl_wait_prior();
-  const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
-  const int b = tok_seq[t], row0 = cu[b], local = t - row0;
-  const float* hist = state + (size_t)seq_slot[b] * (K - 1) * C;
-  float acc = bias ? bias[c] : 0.f;
-  for (int j = 0; j < K; ++j)
-    acc = fmaf(taps[(size_t)c * K + j], filter_input(u, ldu, row0, local - (K - 1) + j, hist, C, c, K), acc);
-  if (act == ACT_SILU) acc = silu_f(acc);
-  out[(size_t)t * ldo + c] = from_f32<O>(acc);
+  float w[MAX_TAPS], win[MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) w[j] = j < K ? taps[(size_t)c * K + j] : 0.f;
+  const float b0 = bias ? bias[c] : 0.f;
+  const int first = blockIdx.x * per, end = min(first + per, ntok);
+  int b = tok_seq[first], row0 = cu[b], next_start = cu[b + 1];
+  {
+    const float* hist = state + (size_t)seq_slot[b] * (K - 1) * C;
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS - 1; ++j)
+      win[j] = j < K - 1 ? filter_input(u, ldu, row0, first - row0 - (K - 1) + j, hist, C, c, K) : 0.f;
+  }
+  const T* in = u + (size_t)first * ldu + c;
+  O* o = out + (size_t)first * ldo + c;
+  for (int t = first; t < end; ++t, in += ldu, o += ldo) {
+    if (t == next_start) {                      // the next sequence of the step starts here
+      ++b;
+      next_start = cu[b + 1];
+      const float* hist = state + (size_t)seq_slot[b] * (K - 1) * C;
+#pragma unroll
+      for (int j = 0; j < MAX_TAPS - 1; ++j) win[j] = j < K - 1 ? hist[(size_t)j * C + c] : 0.f;
+    }
+    const float now = to_f32(*in);
+    float acc = b0;
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS - 1; ++j)
+      if (j < K - 1) acc = fmaf(w[j], win[j], acc);
+    acc = fmaf(taps[(size_t)c * K + K - 1], now, acc);
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS - 1; ++j)
+      if (j < K - 1) win[j] = j + 1 < K - 1 ? win[j + 1] : now;
+    if (act == ACT_SILU) acc = silu_f(acc);
+    *o = from_f32<O>(acc);
+  }
 }
 
 // The state after the step: the last K-1 inputs of the sequence, old rows shifted where the step
@@ -103,7 +136,8 @@ GB_EXPORT int gb_short_filter(const void* u, int in_dtype, long long ldu, const 
                               int ntok, int nseq, int C, int K, int act, int update_state, cudaStream_t stream) {
   if (ntok <= 0) return 0;
   if (K < 1 || K > MAX_TAPS || C <= 0) return GB_ERR_SIZE;
-  dim3 grid(ntok, (C + 255) / 256), sgrid(nseq, (C + 255) / 256);
+  const int per = ntok >= 512 ? 16 : 1;        // rows a thread walks: a prompt's, or one of a small step
+  dim3 grid((ntok + per - 1) / per, (C + 255) / 256), sgrid(nseq, (C + 255) / 256);
   if (ntok == nseq && update_state && K > 1) {     // every sequence brings one token
 #define GB_SINGLE(T, O)                                                                                                     \
   gb_launch(short_filter_single_kernel<T, O>, sgrid, 256, 0, stream, (const T*)u, ldu, taps, bias, state, seq_slot, (O*)out, ldo, \
@@ -118,7 +152,7 @@ GB_EXPORT int gb_short_filter(const void* u, int in_dtype, long long ldu, const 
   }
 #define GB_FILTER(T, O)                                                                                                   \
   gb_launch(short_filter_kernel<T, O>, grid, 256, 0, stream, (const T*)u, ldu, taps, bias, (const float*)state, cu, tok_seq, \
-            seq_slot, (O*)out, ldo, C, K, act)
+            seq_slot, (O*)out, ldo, ntok, per, C, K, act)
   if (in_dtype == GB_F32 && out_dtype == GB_F32) GB_FILTER(float, float);
   else if (in_dtype == GB_F32 && out_dtype == GB_BF16) GB_FILTER(float, bf16);
   else if (in_dtype == GB_BF16 && out_dtype == GB_BF16) GB_FILTER(bf16, bf16);

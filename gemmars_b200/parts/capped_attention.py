@@ -43,6 +43,8 @@ class CappedAttention(Part):
         self.out_scale = float(p.get("out_scale", 1.0))
         if self.heads % self.kv_heads:
             raise ValueError(f"capped_attention: {self.heads} heads are not a multiple of {self.kv_heads} kv heads")
+        if self.dim > 512:
+            raise ValueError(f"capped_attention: keys of {self.dim} are wider than the kernels take (512)")
         if self.vdim > 512:
             raise ValueError(f"capped_attention: values of {self.vdim} are wider than the kernel takes (512)")
         if not 0 <= self.taps <= 8:

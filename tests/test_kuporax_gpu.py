@@ -149,6 +149,49 @@ def test_short_filter_carries_its_last_inputs(taps, bias, act, dtype):
             state[s].zero_()                          # what opening a sequence does
 
 
+@pytest.mark.parametrize("taps", [2, 4, 7])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_filter_over_a_long_step_of_several_sequences(taps, dtype):
+    """A step of more than 512 rows, in which a thread walks sixteen rows with the window in its
+    registers: sequences of 300, 5, 260, 1 and 40 rows that each go on from a memory of earlier
+    inputs, so the window has to be read anew wherever the rows pass to the next sequence; then
+    the same rows one sequence a step, which must give the same bits."""
+    from gemmars_b200 import kernels
+    rng = np.random.default_rng(taps)
+    c, lens, slots = 300, [300, 5, 260, 1, 40], [3, 0, 4, 1, 2]
+    w, wn = _rand(rng, (c, taps))
+    b, bn = _rand(rng, (c,))
+    before = [_rand(rng, (taps - 1, c), _dt(dtype)) for _ in lens]        # what each sequence brought earlier
+    rows = [_rand(rng, (n, c), _dt(dtype)) for n in lens]
+    want = [plain.silu(plain.short_conv(np.concatenate([h[1], x[1]]), wn, bn))[taps - 1:] for h, x in zip(before, rows)]
+
+    def fresh_state():
+        state = torch.zeros((6, taps - 1, c), dtype=torch.float32, device=DEV)
+        for h, s_ in zip(before, slots):
+            state[s_] = h[0].float()
+        return state
+
+    state = fresh_state()
+    cu, seq, slot, _ = _packed(lens, slots)
+    out = torch.empty((sum(lens), c), dtype=_dt(dtype), device=DEV)
+    kernels.short_filter(torch.cat([x[0] for x in rows]), w, b, state, cu, seq, slot, out, act=True)
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    got = out.double().cpu().numpy()
+    assert np.abs(got - np.concatenate(want)).max() < tol * max(1.0, np.abs(np.concatenate(want)).max())
+    for x, s_, n in zip(rows, slots, lens):
+        tail = np.concatenate([before[slots.index(s_)][1], x[1]])[-(taps - 1):]
+        assert np.abs(state[s_].double().cpu().numpy() - tail).max() < 1e-6
+    state2 = fresh_state()
+    at = 0
+    for x, s_, n in zip(rows, slots, lens):
+        cu1, seq1, slot1, _ = _packed([n], [s_])
+        one = torch.empty((n, c), dtype=_dt(dtype), device=DEV)
+        kernels.short_filter(x[0], w, b, state2, cu1, seq1, slot1, one, act=True)
+        assert torch.equal(one, out[at:at + n])
+        at += n
+    assert torch.equal(state, state2)
+
+
 @pytest.mark.parametrize("heads,groups,dim,vdim", [(4, 4, 16, 24), (6, 2, 8, 40), (3, 1, 64, 64), (2, 2, 128, 128), (1, 1, 20, 7), (2, 1, 200, 72)])
 def test_delta_rule_alone(heads, groups, dim, vdim):
     """Whole sequences against portions of 1, 2, 5 and 33 tokens, in slots out of order; the unit
