@@ -323,6 +323,24 @@ __global__ void __launch_bounds__(32 * P) delta_rule_kernel(const float* __restr
   }
 }
 
+// A scan of few blocks (a prompt of one or two sequences) is launched without the attribute that lets
+// it start under the kernel before it.  Started early, its blocks are placed on whichever SMs have room
+// at that moment, several to an SM, and then share that SM's shared-memory bandwidth for the whole walk:
+// measured, a 2,048-token prompt of four layers took 8.5 ms against 6.4 when the kernel before the scans
+// became one of fewer, longer blocks.  Started when the GPU is idle, the blocks spread one to an SM.
+template <typename Kernel, typename... Args>
+static inline void launch_scan(Kernel kernel, dim3 grid, dim3 block, cudaStream_t stream, Args&&... args) {
+  if ((size_t)grid.x * grid.y * grid.z > 2 * 148) {
+    gb_launch(kernel, grid, block, 0, stream, static_cast<Args&&>(args)...);
+    return;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.stream = stream;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<Args&&>(args)...);
+}
+
 static inline int lanes_for(int dims) { return dims <= SLICE ? 1 : (dims <= 2 * SLICE ? 2 : (dims <= 4 * SLICE ? 4 : 8)); }
 
 // Floats of one head's state for columns of ``dims`` (what a caller allocates per slot and head).
@@ -337,8 +355,8 @@ GB_EXPORT int gb_delta_rule(const float* q, const float* k, const float* v, long
   if (G <= 0 || H % G || V <= 0 || D <= 0 || D > 8 * SLICE || ((uintptr_t)state & 15)) return GB_ERR_SIZE;
   dim3 grid(nseq, H, (V + 31) / 32);
 #define GB_DELTA(P)                                                                                                    \
-  gb_launch(delta_rule_kernel<P>, grid, 32 * P, 0, stream, q, k, v, ld, beta_logit, a_logit, ldg, A_log, dt_bias, state, cu, \
-            seq_slot, y, H, G, D, V, qscale)
+  launch_scan(delta_rule_kernel<P>, grid, 32 * P, stream, q, k, v, ld, beta_logit, a_logit, ldg, A_log, dt_bias, state, cu, \
+              seq_slot, y, H, G, D, V, qscale)
   switch (lanes_for(D)) {
     case 1: GB_DELTA(1); break;
     case 2: GB_DELTA(2); break;
@@ -444,8 +462,8 @@ GB_EXPORT int gb_ssd_scan(const float* x, const float* Bm, const float* Cm, long
   if (G <= 0 || H % G || V <= 0 || N <= 0 || N > 8 * SLICE || ((uintptr_t)state & 15)) return GB_ERR_SIZE;
   dim3 grid(nseq, H, (V + 31) / 32);
 #define GB_SSD(P)                                                                                                       \
-  gb_launch(ssd_scan_kernel<P>, grid, 32 * P, 0, stream, x, Bm, Cm, ld, dt_raw, ldd, A_log, dt_bias, skip, state, cu, seq_slot, y, \
-            H, G, N, V)
+  launch_scan(ssd_scan_kernel<P>, grid, 32 * P, stream, x, Bm, Cm, ld, dt_raw, ldd, A_log, dt_bias, skip, state, cu, seq_slot, y, \
+              H, G, N, V)
   switch (lanes_for(N)) {
     case 1: GB_SSD(1); break;
     case 2: GB_SSD(2); break;
