@@ -380,9 +380,23 @@ GB_EXPORT int gb_attention_capped_mma(const void* q, long long q_stride, void* o
       cudaFuncSetAttribute(attention_capped_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       raised = true;
     }
-    gb_launch(attention_capped_single_kernel, dim3(n_seqs, nkv * ((rep + 15) / 16)), SPLIT * 32, smem, stream,
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, kv, cu_seqlens,
-        seq_start, seq_slot, n_seqs, nh, window, scale, cap, (const bf16*)gate, gate_stride, out_scale);
+    const dim3 sgrid(n_seqs, nkv * ((rep + 15) / 16));
+    if ((size_t)sgrid.x * sgrid.y > 2 * 148) {
+      gb_launch(attention_capped_single_kernel, sgrid, SPLIT * 32, smem, stream,
+          (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, kv, cu_seqlens,
+          seq_start, seq_slot, n_seqs, nh, window, scale, cap, (const bf16*)gate, gate_stride, out_scale);
+    } else {
+      // few CTAs: started only when the kernel before has ended, so that they spread one to an SM instead of
+      // sharing the few SMs that had room while that kernel ran
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = sgrid;
+      cfg.blockDim = dim3(SPLIT * 32);
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = stream;
+      cudaLaunchKernelEx(&cfg, attention_capped_single_kernel,
+          (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, kv, cu_seqlens,
+          seq_start, seq_slot, n_seqs, nh, window, scale, cap, (const bf16*)gate, gate_stride, out_scale);
+    }
     return gb_launch_status();
   }
   dim3 grid((ntok + TILE - 1) / TILE + n_seqs, nkv * chunks);
